@@ -176,6 +176,9 @@ class CacheManager:
             if getattr(spec, "paged", False):
                 g = self.groups[self.run_group[i]]
                 self.kv[i] = spec.allocate(g.pool.num_pages, g.page_size, dtype, device)
+                extra = getattr(spec, "state", None)          # a paged run that also keeps a state of fixed size
+                if extra is not None:
+                    self.state[i] = extra.allocate(self.max_requests, self.page_size, dtype, device)
             else:
                 self.state[i] = spec.allocate(self.max_requests, self.page_size, dtype, device)
         self.tables_dev = [torch.from_numpy(t).to(device) for t in self.tables]
@@ -223,7 +226,8 @@ class CacheManager:
             self.tables_dev[gi].view(-1).index_copy_(0, dev[0], dev[1].to(torch.int32))
         for slot in self._new_slots:
             for run, st in self.state.items():
-                if getattr(self.specs[run][0], "zero_on_start", True):
+                spec = self.specs[run][0]
+                if getattr(getattr(spec, "state", None) or spec, "zero_on_start", True):
                     st[slot].zero_()
         self._new_slots = []
 

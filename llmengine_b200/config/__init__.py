@@ -11,6 +11,7 @@ from .bepuzen import BepuzenConfig
 from .qwen3 import ConfigError, Qwen3Config
 from .spec import LayerRun, LayerSpec, ModelSpec, PartSpec
 from .torisun import TorisunConfig
+from .vifelix import VifelixConfig
 
 
 @dataclass(frozen=True)
@@ -69,6 +70,7 @@ def load_config(model_dir: str):
 register_architecture(Qwen3Config.ARCHITECTURE, Qwen3Config)
 register_architecture(BepuzenConfig.ARCHITECTURE, BepuzenConfig)
 register_architecture(TorisunConfig.ARCHITECTURE, TorisunConfig)
+register_architecture(VifelixConfig.ARCHITECTURE, VifelixConfig)
 
 
 @dataclass
@@ -117,5 +119,5 @@ class EngineConfig:
 
 __all__ = [
     "ARCHITECTURES", "Architecture", "BepuzenConfig", "ConfigError", "EngineConfig", "LayerRun", "LayerSpec", "ModelSpec",
-    "PartSpec", "Qwen3Config", "TorisunConfig", "config_from_dict", "find_architecture", "load_config", "register_architecture",
+    "PartSpec", "Qwen3Config", "TorisunConfig", "VifelixConfig", "config_from_dict", "find_architecture", "load_config", "register_architecture",
 ]

@@ -77,6 +77,75 @@ __global__ void window_post_kernel(LlmeWindowPostArgs a) {
     }
 }
 
+// The same step for designs that norm every head by itself (gains of one head's size, shared by the heads) and whose
+// projections have biases: one warp per (token, head); the biased head is read twice (sum of squares, then the values).
+// The value may be the key's own projection (v_in = k_in): it is stored as projected, with its bias, before the norm.
+template <typename T>
+__device__ __forceinline__ void finish_head(const T* __restrict__ in, const float* __restrict__ bias, const float* __restrict__ gain, float eps, int dk,
+                                            const float* __restrict__ inv_freq, int dims, float amp, int position, T* __restrict__ out, int lane) {
+    auto raw = [&](int j) -> float {
+        const float v = to_f32(in[j]);
+        return bias ? to_f32(from_f32<T>(v + bias[j])) : v;      // a projection's output has the type of the products
+    };
+    float rinv = 1.0f;
+    if (gain) {
+        float ss = 0.0f;
+        for (int j = lane; j < dk; j += 32) {
+            const float v = raw(j);
+            ss += v * v;
+        }
+        rinv = 1.0f / sqrtf(warp_sum(ss) / (float)dk + eps);
+    }
+    auto normed = [&](int j) -> float { return gain ? (raw(j) * rinv) * gain[j] : raw(j); };
+    const int half = dims >> 1;
+    for (int d = lane; d < dk; d += 32) {
+        float v;
+        if (!inv_freq || d >= dims) v = normed(d);
+        else {
+            const int i = d < half ? d : d - half;
+            float s, c;
+            sincosf((float)position * inv_freq[i], &s, &c);
+            s *= amp;
+            c *= amp;
+            const float u = normed(i), w = normed(i + half);
+            v = d < half ? u * c - w * s : w * c + u * s;
+        }
+        out[d] = from_f32<T>(v);
+    }
+}
+
+template <typename T>
+__global__ void window_post_heads_kernel(LlmeWindowPostArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+    const int item = blockIdx.x * warps + (threadIdx.x >> 5);       // (token, head of q | head of k | head of v)
+    const bool stores = a.k_in != nullptr;
+    const int per_token = a.nh + (stores ? 2 * a.nkv : 0);
+    if (item >= a.tokens * per_token) return;
+    const int t = item / per_token, hh = item - t * per_token;
+    const int dk = a.dk, dv = a.dv, ps = a.page_size, pos = a.positions[t];
+    if (hh < a.nh) {
+        finish_head((const T*)a.q_in + (size_t)t * a.q_stride + hh * dk, a.q_bias ? a.q_bias + hh * dk : nullptr, a.q_gain, a.eps, dk,
+                    a.inv_freq, a.rot_dims, a.amplitude, pos, (T*)a.q_out + ((size_t)t * a.nh + hh) * dk, lane);
+        return;
+    }
+    const int slot = a.slot_mapping[t];
+    if (slot < 0) return;
+    const int page = slot / ps, off = slot - page * ps;
+    T* kpage = (T*)a.cache + (size_t)page * ((size_t)a.nkv * ps * (dk + dv));
+    if (hh < a.nh + a.nkv) {
+        const int g = hh - a.nh;
+        finish_head((const T*)a.k_in + (size_t)t * a.k_stride + g * dk, a.k_bias ? a.k_bias + g * dk : nullptr, a.k_gain, a.eps, dk,
+                    a.inv_freq, a.rot_dims, a.amplitude, pos, kpage + ((size_t)g * ps + off) * dk, lane);
+        return;
+    }
+    const int g = hh - a.nh - a.nkv;
+    const T* v = (const T*)a.v_in + (size_t)t * a.v_stride + g * dv;
+    T* vo = kpage + (size_t)a.nkv * ps * dk + ((size_t)g * ps + off) * dv;
+    for (int d = lane; d < dv; d += 32) vo[d] = a.v_bias ? from_f32<T>(to_f32(v[d]) + a.v_bias[g * dv + d]) : v[d];
+}
+
 LLME_API int llme_window_post(const LlmeWindowPostArgs* args, int dtype, cudaStream_t stream) {
     const LlmeWindowPostArgs& a = *args;
     if (a.tokens <= 0) return 0;
@@ -87,6 +156,15 @@ LLME_API int llme_window_post(const LlmeWindowPostArgs* args, int dtype, cudaStr
     if (a.inv_freq && (a.rot_dims <= 0 || a.rot_dims % 2 || a.rot_dims > a.dk))
         LLME_REFUSE("window_post: %d rotated coordinates of %d need an even count", a.rot_dims, a.dk);
     if ((a.q_gain || a.k_gain) && !(a.eps > 0.0f)) LLME_REFUSE("window_post: eps must be positive");
+    if (a.head_norm || a.q_bias || a.k_bias || a.v_bias) {
+        if (!a.head_norm && (a.q_gain || a.k_gain)) LLME_REFUSE("window_post: biases come with the norm per head or with no norm");
+        const long long items = (long long)a.tokens * (a.nh + (a.k_in ? 2 * a.nkv : 0));
+        const int wpb = 4;
+        if (dtype == LLME_F32) llme_launch(window_post_heads_kernel<float>, dim3((unsigned)((items + wpb - 1) / wpb)), dim3(wpb * 32), 0, stream, a);
+        else if (dtype == LLME_BF16) llme_launch(window_post_heads_kernel<__nv_bfloat16>, dim3((unsigned)((items + wpb - 1) / wpb)), dim3(wpb * 32), 0, stream, a);
+        else LLME_REFUSE("window_post: unsupported dtype %d", dtype);
+        LLME_LAUNCH_STATUS();
+    }
     const int qn = a.nh * a.dk;
     const int threads = qn >= 2048 ? 512 : (qn >= 512 ? 256 : 128);
     if (dtype == LLME_F32) llme_launch(window_post_kernel<float>, dim3(a.tokens), dim3(threads), 0, stream, a);

@@ -13,11 +13,12 @@
 LLME_API const char* llme_last_error() { return llme_error_buffer(); }
 
 // ----------------------------------------------------------------------------- embedding
-// out[t, :] = float(table[ids[t], :]).  An id outside the table gives a row of zeros here;
-// the engine refuses such ids on the host before it launches anything.
+// out[t, :] = float(table[ids[t], :]) * scale (a design may scale its embedding by a constant; 1 for none; the
+// product is formed in 32-bit).  An id outside the table gives a row of zeros here; the engine refuses such ids on
+// the host before it launches anything.
 template <typename W>
 __global__ void embedding_kernel(const int* __restrict__ ids, const W* __restrict__ table,
-                                 float* __restrict__ out, int hidden, int vocab) {
+                                 float* __restrict__ out, int hidden, int vocab, float scale) {
     pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
     pdl_wait();                // everything below reads or writes what earlier kernels touch
     const int t = blockIdx.x;
@@ -28,12 +29,12 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const W* __restric
         return;
     }
     const W* row = table + (size_t)id * hidden;
-    for (int j = threadIdx.x; j < hidden; j += blockDim.x) o[j] = to_f32(row[j]);
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) o[j] = to_f32(row[j]) * scale;
 }
 
 // The same for bfloat16 tables whose rows are a multiple of 8 wide: 16 bytes in, 32 bytes out per thread.
 __global__ void embedding_bf16x8_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
-                                        float* __restrict__ out, int hidden, int vocab) {
+                                        float* __restrict__ out, int hidden, int vocab, float scale) {
     pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
     pdl_wait();                // everything below reads or writes what earlier kernels touch
     const int t = blockIdx.x;
@@ -48,30 +49,35 @@ __global__ void embedding_bf16x8_kernel(const int* __restrict__ ids, const __nv_
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
             const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]);
             const float2 f2 = __bfloat1622float2(h[2]), f3 = __bfloat1622float2(h[3]);
-            a = make_float4(f0.x, f0.y, f1.x, f1.y);
-            b = make_float4(f2.x, f2.y, f3.x, f3.y);
+            a = make_float4(f0.x * scale, f0.y * scale, f1.x * scale, f1.y * scale);
+            b = make_float4(f2.x * scale, f2.y * scale, f3.x * scale, f3.y * scale);
         }
         o[2 * j] = a;
         o[2 * j + 1] = b;
     }
 }
 
-LLME_API int llme_embedding(const int* ids, const void* table, int table_dtype, float* out,
-                            int tokens, int hidden, int vocab, cudaStream_t stream) {
+LLME_API int llme_embedding_scaled(const int* ids, const void* table, int table_dtype, float* out,
+                                   int tokens, int hidden, int vocab, float scale, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (!ids || !table || !out || hidden <= 0 || vocab <= 0) LLME_REFUSE("embedding: null pointer or non-positive size");
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == LLME_BF16 && hidden % 8 == 0 && ((uintptr_t)table % 16) == 0 && ((uintptr_t)out % 16) == 0) {
-        llme_launch(embedding_bf16x8_kernel, dim3(tokens), dim3(hidden >= 2048 ? 256 : 64), 0, stream, ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+        llme_launch(embedding_bf16x8_kernel, dim3(tokens), dim3(hidden >= 2048 ? 256 : 64), 0, stream, ids, (const __nv_bfloat16*)table, out, hidden, vocab, scale);
         LLME_LAUNCH_STATUS();
     }
     if (table_dtype == LLME_F32)
-        llme_launch(embedding_kernel<float>, dim3(tokens), dim3(threads), 0, stream, ids, (const float*)table, out, hidden, vocab);
+        llme_launch(embedding_kernel<float>, dim3(tokens), dim3(threads), 0, stream, ids, (const float*)table, out, hidden, vocab, scale);
     else if (table_dtype == LLME_BF16)
-        llme_launch(embedding_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+        llme_launch(embedding_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, ids, (const __nv_bfloat16*)table, out, hidden, vocab, scale);
     else
         LLME_REFUSE("embedding: unsupported table dtype %d", table_dtype);
     LLME_LAUNCH_STATUS();
+}
+
+LLME_API int llme_embedding(const int* ids, const void* table, int table_dtype, float* out,
+                            int tokens, int hidden, int vocab, cudaStream_t stream) {
+    return llme_embedding_scaled(ids, table, table_dtype, out, tokens, hidden, vocab, 1.0f, stream);
 }
 
 // ----------------------------------------------------------------------------- RMS norm (+ residual add)

@@ -59,6 +59,14 @@ typedef int (*WindowAttnTcFn)(const LlmeWindowFastArgs*, int, int, cudaStream_t)
 typedef int (*MoeRouteFn)(const LlmeMoeRouteArgs*, cudaStream_t);
 typedef int (*GroupedFn)(const LlmeGroupedArgs*, int, int, int, cudaStream_t);
 typedef int (*MoeCombineFn)(const float*, long long, const float*, const float*, float*, int, int, int, cudaStream_t);
+typedef int (*EmbeddingScaledFn)(const int*, const void*, int, float*, int, int, int, float, cudaStream_t);
+typedef int (*SigmoidMulScaledFn)(const void*, long long, const void*, long long, void*, long long, int, int, int, float, cudaStream_t);
+typedef int (*GatedActBiasFn)(const void*, long long, void*, long long, int, int, int, int, float, float, const float*, cudaStream_t);
+typedef int (*BiasAddFn)(void*, long long, int, const float*, int, int, cudaStream_t);
+typedef int (*ShortConvFn)(const LlmeShortConvArgs*, int, cudaStream_t);
+typedef int (*RotateFn)(const LlmeRotateArgs*, cudaStream_t);
+typedef int (*RecurrenceFn)(const LlmeRecurrenceArgs*, cudaStream_t);
+typedef int (*GatedNormFn)(const LlmeGatedNormArgs*, cudaStream_t);
 typedef int (*GemmF32BatchedFn)(const float*, const void*, int, float*, int, int, int, long long, long long, long long, int, long long,
                                 long long, long long, cudaStream_t);
 
@@ -170,14 +178,19 @@ size_t record_size(int kind) {
         case LLME_OP_MOE_ROUTE: return sizeof(LlmeMoeRouteOp);
         case LLME_OP_GROUPED_LINEAR: return sizeof(LlmeGroupedLinearOp);
         case LLME_OP_MOE_COMBINE: return sizeof(LlmeMoeCombineOp);
+        case LLME_OP_SHORT_CONV: return sizeof(LlmeShortConvOp);
+        case LLME_OP_ROTATE: return sizeof(LlmeRotateOp);
+        case LLME_OP_RECURRENCE: return sizeof(LlmeRecurrenceOp);
+        case LLME_OP_GATED_NORM: return sizeof(LlmeGatedNormOp);
     }
     return 0;
 }
 const char* kind_name(int kind) {
     static const char* names[] = {"?", "embedding", "rmsnorm", "linear", "linear_swiglu", "qkv_post", "attend", "attention", "call",
                                   "linear_act", "pointwise", "batched_linear", "residual_add", "latent_attention", "token_side",
-                                  "postnorm", "window_attention", "moe_route", "grouped_linear", "moe_combine"};
-    return kind >= 1 && kind <= 19 ? names[kind] : names[0];
+                                  "postnorm", "window_attention", "moe_route", "grouped_linear", "moe_combine", "short_conv", "rotate",
+                                  "recurrence", "gated_norm"};
+    return kind >= 1 && kind <= 23 ? names[kind] : names[0];
 }
 
 constexpr int SKINNY_ROWS = 16;      // most rows the weight-streaming product takes (gemm_skinny.cu)
@@ -282,6 +295,11 @@ int product(LlmeExecutor& ex, const LlmeStep& step, const void* x, long long ldx
 }
 
 int op_embedding(LlmeExecutor& ex, const LlmeEmbeddingOp& o, const LlmeStep& s, cudaStream_t st) {
+    if (o.scale != 1.0f) {
+        auto* g = (EmbeddingScaledFn)ex.find("embedding_scaled");
+        if (!g) return ex.fail("no kernel for a scaled embedding is registered");
+        return ex.launched(g(s.token_ids, o.table, o.table_dtype, o.out, s.num_tokens, o.hidden, o.vocab, o.scale, st), "embedding");
+    }
     auto* f = (EmbeddingFn)ex.find("embedding");
     if (!f) return ex.fail("no embedding kernel is registered");
     return ex.launched(f(s.token_ids, o.table, o.table_dtype, o.out, s.num_tokens, o.hidden, o.vocab, st), "embedding");
@@ -299,14 +317,20 @@ int op_linear(LlmeExecutor& ex, const LlmeLinearOp& o, const LlmeStep& s, cudaSt
     if (rows_of(s, o.rows) <= 0) return 0;
     void* out = o.out ? o.out : (void*)s.logits;
     if (!out) return ex.fail("linear: the step has no place for its logits");
-    return product(ex, s, o.x, o.ldx, o.x_dtype, o.w, o.ldw, o.w_dtype, out, o.out ? o.ldo : o.n, o.out ? o.out_dtype : LLME_DT_F32,
-                   rows_of(s, o.rows), o.n, o.k, st);
+    if (int rc = product(ex, s, o.x, o.ldx, o.x_dtype, o.w, o.ldw, o.w_dtype, out, o.out ? o.ldo : o.n, o.out ? o.out_dtype : LLME_DT_F32,
+                         rows_of(s, o.rows), o.n, o.k, st))
+        return rc;
+    if (!o.bias) return 0;
+    auto* add = (BiasAddFn)ex.find("bias_add");
+    if (!add) return ex.fail("linear: no kernel that adds a bias is registered");
+    return ex.launched(add(out, o.out ? o.ldo : o.n, o.out ? o.out_dtype : LLME_DT_F32, o.bias, rows_of(s, o.rows), o.n, st), "bias_add");
 }
 
 int op_linear_swiglu(LlmeExecutor& ex, const LlmeLinearSwigluOp& o, const LlmeStep& s, cudaStream_t st) {
     const int M = s.num_tokens;
     if (M <= 0) return 0;
-    const bool fused = ex.choice("linear_swiglu") == "fused" && ex.choice("linear") != "plain" && o.dtype == LLME_DT_BF16;
+    // biases before the activation: the product with the activation kernel behind it, which adds them
+    const bool fused = ex.choice("linear_swiglu") == "fused" && ex.choice("linear") != "plain" && o.dtype == LLME_DT_BF16 && !o.bias;
     const bool operands_ok = o.k % 8 == 0 && o.ldx % 8 == 0 && o.ldw % 8 == 0 && aligned16(o.x, o.w_gate_up);
     const std::string& dec = ex.choice("linear.decode");
     if (fused && M <= SKINNY_ROWS && operands_ok && (dec == "skinny" || (dec == "auto" && skinny_pays(ex, M, (o.inter + 7) / 8)))) {
@@ -331,6 +355,11 @@ int op_linear_swiglu(LlmeExecutor& ex, const LlmeLinearSwigluOp& o, const LlmeSt
     if (!o.gate_up) return ex.fail("linear_swiglu: the unfused form needs a workspace for gate|up");
     if (int rc = product(ex, s, o.x, o.ldx, o.dtype, o.w_gate_up, o.ldw, o.dtype, o.gate_up, 2LL * o.inter, o.dtype, M, 2 * o.inter, o.k, st))
         return rc;
+    if (o.bias) {
+        auto* g = (GatedActBiasFn)ex.find("gated_act_bias");
+        if (!g) return ex.fail("no gated activation kernel with biases is registered");
+        return ex.launched(g(o.gate_up, 2LL * o.inter, o.out, o.ldo, o.dtype, M, o.inter, o.act, o.p0, o.p1, o.bias, st), "gated_act");
+    }
     if (o.act != LLME_GATE_SILU) {
         auto* g = (GatedActFn)ex.find("gated_act");
         if (!g) return ex.fail("no gated activation kernel is registered");
@@ -505,6 +534,11 @@ int op_linear_act(LlmeExecutor& ex, const LlmeLinearActOp& o, const LlmeStep& s,
 int op_pointwise(LlmeExecutor& ex, const LlmePointwiseOp& o, const LlmeStep& s, cudaStream_t st) {
     if (s.num_tokens <= 0) return 0;
     if (o.what != LLME_POINTWISE_SIGMOID_MUL) return ex.fail("pointwise: unknown operation %d", o.what);
+    if (o.scale != 1.0f) {
+        auto* g = (SigmoidMulScaledFn)ex.find("sigmoid_mul_scaled");
+        if (!g) return ex.fail("no scaled sigmoid_mul kernel is registered");
+        return ex.launched(g(o.a, o.lda, o.b, o.ldb, o.out, o.ldo, o.dtype, s.num_tokens, o.cols, o.scale, st), "sigmoid_mul");
+    }
     auto* f = (SigmoidMulFn)ex.find("sigmoid_mul");
     if (!f) return ex.fail("no sigmoid_mul kernel is registered");
     return ex.launched(f(o.a, o.lda, o.b, o.ldb, o.out, o.ldo, o.dtype, s.num_tokens, o.cols, st), "sigmoid_mul");
@@ -630,6 +664,7 @@ int op_window_attention(LlmeExecutor& ex, const LlmeWindowAttentionOp& o, const 
     p.q_gain = o.q_gain; p.k_gain = o.k_gain; p.eps = o.eps; p.inv_freq = o.inv_freq; p.rot_dims = o.rot_dims; p.amplitude = o.amplitude;
     p.positions = s.positions; p.q_out = o.q; p.cache = o.cache; p.slot_mapping = g.slot_mapping;
     p.tokens = s.num_tokens; p.nh = o.nh; p.nkv = o.nkv; p.dk = o.dk; p.dv = o.dv; p.page_size = g.page_size;
+    p.q_bias = o.q_bias; p.k_bias = o.k_bias; p.v_bias = o.v_bias; p.head_norm = o.head_norm;
     if (int rc = ex.launched(post(&p, o.dtype, st), "window_post")) return rc;
     // bfloat16 with sizes the tensor-core kernel is built for: prompt portions in one launch, single tokens in another
     auto* tc = (WindowAttnTcFn)ex.find("window_attention_tc/" + std::to_string(o.dk) + "x" + std::to_string(o.dv));
@@ -663,6 +698,47 @@ int op_window_attention(LlmeExecutor& ex, const LlmeWindowAttentionOp& o, const 
     LlmeWindowAttnArgs a = {o.q, o.cache, o.out, o.sink, s.positions, s.token_request, g.block_tables, g.max_blocks, s.num_tokens,
                             o.nh, o.nkv, o.dk, o.dv, g.page_size, o.window, o.keep_first, o.scale};
     return ex.launched(plain(&a, o.dtype, st), "window_attention_plain");
+}
+
+int op_short_conv(LlmeExecutor& ex, const LlmeShortConvOp& o, const LlmeStep& s, cudaStream_t st) {
+    if (s.num_tokens <= 0) return 0;
+    auto* f = (ShortConvFn)ex.find("short_conv");
+    if (!f) return ex.fail("no short_conv kernel is registered");
+    LlmeShortConvArgs a = {o.x, o.ldx, o.x_dtype, o.w, o.bias, o.state, o.state_stride, o.out, o.ldo, s.cu_q_lens, s.state_slots,
+                           s.num_tokens, s.num_requests, o.channels, o.taps, o.act};
+    if (int rc = ex.launched(f(&a, 0, st), "short_conv")) return rc;
+    if (o.taps <= 1) return 0;
+    return ex.launched(f(&a, 1, st), "short_conv");     // after the outputs, which read the state: it takes the step's last inputs
+}
+
+int op_rotate(LlmeExecutor& ex, const LlmeRotateOp& o, const LlmeStep& s, cudaStream_t st) {
+    if (s.num_tokens <= 0) return 0;
+    auto* f = (RotateFn)ex.find("rotate");
+    if (!f) return ex.fail("no rotate kernel is registered");
+    LlmeRotateArgs a = {};
+    for (int i = 0; i < 2; ++i) {
+        a.x[i] = o.x[i]; a.ldx[i] = o.ldx[i]; a.out[i] = o.out[i]; a.ldo[i] = o.ldo[i]; a.heads[i] = o.heads[i]; a.scale[i] = o.scale[i];
+    }
+    a.dtype = o.dtype; a.dim = o.dim; a.rot_dims = o.rot_dims; a.inv_freq = o.inv_freq; a.positions = s.positions; a.tokens = s.num_tokens;
+    return ex.launched(f(&a, st), "rotate");
+}
+
+int op_recurrence(LlmeExecutor& ex, const LlmeRecurrenceOp& o, const LlmeStep& s, cudaStream_t st) {
+    if (s.num_tokens <= 0 || s.num_requests <= 0) return 0;
+    auto* f = (RecurrenceFn)ex.find("recurrence");
+    if (!f) return ex.fail("no recurrence kernel is registered");
+    LlmeRecurrenceArgs a = {o.q, o.k, o.ldq, o.ldk, o.qk_groups, o.v, o.ldv, o.v_dtype, o.gate, o.decay, o.dt, o.lddt, o.dt_dtype, o.dt_bias,
+                            o.a_log, o.skip, o.state, o.state_stride, o.out, o.ldo, s.cu_q_lens, s.state_slots, s.num_requests, o.heads,
+                            o.n, o.p};
+    return ex.launched(f(&a, st), "recurrence");
+}
+
+int op_gated_norm(LlmeExecutor& ex, const LlmeGatedNormOp& o, const LlmeStep& s, cudaStream_t st) {
+    if (s.num_tokens <= 0) return 0;
+    auto* f = (GatedNormFn)ex.find("gated_norm");
+    if (!f) return ex.fail("no gated_norm kernel is registered");
+    LlmeGatedNormArgs a = {o.y, o.ldy, o.gate, o.ldg, o.weight, o.out, o.ldo, o.dtype, s.num_tokens, o.cols, o.group, o.gate_first, o.eps, o.scale};
+    return ex.launched(f(&a, st), "gated_norm");
 }
 
 int op_moe_route(LlmeExecutor& ex, const LlmeMoeRouteOp& o, const LlmeStep& s, cudaStream_t st) {
@@ -844,6 +920,10 @@ LLME_EXPORT int llme_plan_run(LlmePlan* p, const LlmeStep* step, int first, int 
             case LLME_OP_MOE_ROUTE: rc = op_moe_route(ex, *(const LlmeMoeRouteOp*)b, s, stream); break;
             case LLME_OP_GROUPED_LINEAR: rc = op_grouped_linear(ex, *(const LlmeGroupedLinearOp*)b, s, stream); break;
             case LLME_OP_MOE_COMBINE: rc = op_moe_combine(ex, *(const LlmeMoeCombineOp*)b, s, stream); break;
+            case LLME_OP_SHORT_CONV: rc = op_short_conv(ex, *(const LlmeShortConvOp*)b, s, stream); break;
+            case LLME_OP_ROTATE: rc = op_rotate(ex, *(const LlmeRotateOp*)b, s, stream); break;
+            case LLME_OP_RECURRENCE: rc = op_recurrence(ex, *(const LlmeRecurrenceOp*)b, s, stream); break;
+            case LLME_OP_GATED_NORM: rc = op_gated_norm(ex, *(const LlmeGatedNormOp*)b, s, stream); break;
             case LLME_OP_CALL: {
                 const LlmeCallOp& c = *(const LlmeCallOp*)b;
                 rc = c.fn ? c.fn(c.user, step, stream) : 0;

@@ -79,6 +79,10 @@ typedef struct LlmeWindowPostArgs {
     void* q_out;                                             /* [T, nh * dk] */
     void* cache; const int* slot_mapping;
     int tokens, nh, nkv, dk, dv, page_size;
+    /* options of other designs (all off when zero): biases of the three projections, added first (32-bit, [nh * dk],
+     * [nkv * dk], [nkv * dv]); `head_norm` 1: every head is normed by itself and the gains are [dk], shared by the heads */
+    const float* q_bias; const float* k_bias; const float* v_bias;
+    int head_norm;
 } LlmeWindowPostArgs;
 
 /* Attention over such a cache: query i sees key j if j <= i and (i - j < window or j < keep_first). */
@@ -119,3 +123,55 @@ typedef struct LlmeGroupedArgs {
     int gather, scatter;                                     /* x row = order[r] / top_k; out row = order[r] */
     int act;                                                 /* 1: w[e] = [gate | up], the row written is silu(gate) * up, n / 2 wide */
 } LlmeGroupedArgs;
+
+/* Causal convolution per channel over the tokens of each request (csrc/recurrent.cu): y_t = bias + sum_j w[:, K-1-j] x_(t-j),
+ * then the activation; the last K - 1 inputs of every request are carried in its state slot ([K - 1, channels], oldest first,
+ * zero for a request that starts: the zeros before the start).  Two launches: `update` 0: the outputs of the step's tokens (the state is
+ * read); 1: the state takes the step's last inputs (a launch of its own, after the first). */
+typedef struct LlmeShortConvArgs {
+    const void* x; long long ldx; int x_dtype;               /* [T, channels] (a column range of a product) */
+    const float* w; const float* bias;                       /* [channels, taps]; [channels] or NULL */
+    float* state; long long state_stride;                    /* slot s: state + s * state_stride */
+    float* out; long long ldo;                               /* [T, channels] 32-bit */
+    const int* cu_q_lens; const int* state_slots;
+    int tokens, requests, channels, taps, act;               /* act 1: silu */
+} LlmeShortConvArgs;
+
+/* Rotation of the first rot_dims coordinates of every head (rotate-half pairs, angle position * inv_freq[i], 32-bit) of up
+ * to two tensors, each times a constant afterwards; the results are 32-bit. */
+typedef struct LlmeRotateArgs {
+    const void* x[2]; long long ldx[2]; float* out[2]; long long ldo[2]; int heads[2]; float scale[2];   /* x[i] NULL: absent */
+    int dtype, dim, rot_dims;
+    const float* inv_freq; const int* positions;
+    int tokens;
+} LlmeRotateArgs;
+
+/* A linear recurrence with a decaying matrix state per head and request (csrc/recurrent.cu):
+ *   S_t = a_t S_(t-1) + s_t k_t v_t^T   (S is n x p),   y_t = S_t^T q_t + skip_h v_t.
+ * gate 0: a_t = decay[h], s_t = 1.  gate 1: d = softplus(dt[t, h] + dt_bias[h]), a_t = exp(-exp(a_log[h]) d), s_t = d.
+ * q and k come in `qk_groups` groups of n; head h reads group h / (heads / qk_groups).  The state lives in 32-bit in the
+ * request's slot, one column of S after the other ([heads, p, n]), and goes from step to step. */
+typedef struct LlmeRecurrenceArgs {
+    const float* q; const float* k; long long ldq, ldk; int qk_groups;
+    const void* v; long long ldv; int v_dtype;               /* [T, heads * p] */
+    int gate;
+    const float* decay;
+    const void* dt; long long lddt; int dt_dtype; const float* dt_bias; const float* a_log;
+    const float* skip;                                       /* [heads] or NULL */
+    float* state; long long state_stride;                    /* slot s: [heads, p, n] at state + s * state_stride */
+    float* out; long long ldo;                               /* [T, heads * p] 32-bit */
+    const int* cu_q_lens; const int* state_slots;
+    int requests, heads, n, p;
+} LlmeRecurrenceArgs;
+
+/* RMS norm in groups of `group` columns with a gate (silu of a second tensor) before or after it:
+ * gate_first 1: u = y silu(g), out = u / rms(u) * weight;  0: out = y / rms(y) * weight * silu(g); then times `scale`.
+ * weight NULL: none.  y is 32-bit; g and out have `dtype`. */
+typedef struct LlmeGatedNormArgs {
+    const float* y; long long ldy;
+    const void* gate; long long ldg;
+    const float* weight;
+    void* out; long long ldo;
+    int dtype, tokens, cols, group, gate_first;
+    float eps, scale;
+} LlmeGatedNormArgs;

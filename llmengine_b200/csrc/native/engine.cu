@@ -933,7 +933,7 @@ private:
         const long long qs = (long long)nh * hd, kvs = (long long)nkv * hd;
         const float eps = (float)c.rms_norm_eps;
         plan_ = x_.plan_create(ex_);
-        LlmeEmbeddingOp emb = {embedding_.ptr, embedding_.dtype, c.vocab_size, H, (float*)x_buf_.ptr};
+        LlmeEmbeddingOp emb = {embedding_.ptr, embedding_.dtype, c.vocab_size, H, (float*)x_buf_.ptr, 1.0f};
         add(LLME_OP_EMBEDDING, emb);
         const void* delta = nullptr;
         const size_t item = dt_ == LLME_DT_BF16 ? 2 : 4;

@@ -71,28 +71,33 @@ LLME_API int llme_xielu(const void* in, long long ld_in, void* out, long long ld
     LLME_LAUNCH_STATUS();
 }
 
-// ----------------------------------------------------------------------------- out = a * sigmoid(b)
+// ----------------------------------------------------------------------------- out = a * sigmoid(b) * scale
 template <typename T>
 __global__ void sigmoid_mul_kernel(const T* __restrict__ a, long long lda, const T* __restrict__ b, long long ldb, T* __restrict__ out,
-                                   long long ldo, int cols) {
+                                   long long ldo, int cols, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const T* ar = a + (size_t)blockIdx.x * lda;
     const T* br = b + (size_t)blockIdx.x * ldb;
     T* o = out + (size_t)blockIdx.x * ldo;
     for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < cols; j += gridDim.y * blockDim.x)
-        o[j] = from_f32<T>(to_f32(ar[j]) * sigmoid(to_f32(br[j])));
+        o[j] = from_f32<T>((to_f32(ar[j]) * sigmoid(to_f32(br[j]))) * scale);
+}
+
+LLME_API int llme_sigmoid_mul_scaled(const void* a, long long lda, const void* b, long long ldb, void* out, long long ldo, int dtype,
+                                     int rows, int cols, float scale, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (!a || !b || !out) LLME_REFUSE("sigmoid_mul: null pointer");
+    const int threads = 128;
+    if (dtype == LLME_F32) llme_launch(sigmoid_mul_kernel<float>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const float*)a, lda, (const float*)b, ldb, (float*)out, ldo, cols, scale);
+    else if (dtype == LLME_BF16) llme_launch(sigmoid_mul_kernel<__nv_bfloat16>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb, (__nv_bfloat16*)out, ldo, cols, scale);
+    else LLME_REFUSE("sigmoid_mul: unsupported dtype %d", dtype);
+    LLME_LAUNCH_STATUS();
 }
 
 LLME_API int llme_sigmoid_mul(const void* a, long long lda, const void* b, long long ldb, void* out, long long ldo, int dtype,
                               int rows, int cols, cudaStream_t stream) {
-    if (rows <= 0 || cols <= 0) return 0;
-    if (!a || !b || !out) LLME_REFUSE("sigmoid_mul: null pointer");
-    const int threads = 128;
-    if (dtype == LLME_F32) llme_launch(sigmoid_mul_kernel<float>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const float*)a, lda, (const float*)b, ldb, (float*)out, ldo, cols);
-    else if (dtype == LLME_BF16) llme_launch(sigmoid_mul_kernel<__nv_bfloat16>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb, (__nv_bfloat16*)out, ldo, cols);
-    else LLME_REFUSE("sigmoid_mul: unsupported dtype %d", dtype);
-    LLME_LAUNCH_STATUS();
+    return llme_sigmoid_mul_scaled(a, lda, b, ldb, out, ldo, dtype, rows, cols, 1.0f, stream);
 }
 
 // ----------------------------------------------------------------------------- x += a (+ b), optionally a copy of x in another type
@@ -379,23 +384,53 @@ __device__ __forceinline__ float gated_activation(int act, float g, float u, flo
 
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gate_up, long long ld_in, T* __restrict__ out, long long ld_out, int cols, int act, float p0,
-                                 float p1) {
+                                 float p1, const float* __restrict__ bias) {
     pdl_launch_dependents();
     pdl_wait();
     const T* i = gate_up + (size_t)blockIdx.x * ld_in;
     T* o = out + (size_t)blockIdx.x * ld_out;
-    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < cols; j += gridDim.y * blockDim.x)
-        o[j] = from_f32<T>(gated_activation(act, to_f32(i[j]), to_f32(i[cols + j]), p0, p1));
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < cols; j += gridDim.y * blockDim.x) {
+        float g = to_f32(i[j]), u = to_f32(i[cols + j]);
+        if (bias) {                       // the projections' biases [gate | up], added before the activation; each sum
+            g = to_f32(from_f32<T>(g + bias[j]));          // is a projection's output and takes its type
+            u = to_f32(from_f32<T>(u + bias[cols + j]));
+        }
+        o[j] = from_f32<T>(gated_activation(act, g, u, p0, p1));
+    }
 }
 
-LLME_API int llme_gated_act(const void* gate_up, long long ld_in, void* out, long long ld_out, int dtype, int rows, int cols, int act,
-                            float p0, float p1, cudaStream_t stream) {
+LLME_API int llme_gated_act_bias(const void* gate_up, long long ld_in, void* out, long long ld_out, int dtype, int rows, int cols, int act,
+                                 float p0, float p1, const float* bias, cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return 0;
     if (!gate_up || !out) LLME_REFUSE("gated_act: null pointer");
     if (act != 0 && act != 1) LLME_REFUSE("gated_act: unknown activation %d", act);
     const int threads = 128;
-    if (dtype == LLME_F32) llme_launch(gated_act_kernel<float>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const float*)gate_up, ld_in, (float*)out, ld_out, cols, act, p0, p1);
-    else if (dtype == LLME_BF16) llme_launch(gated_act_kernel<__nv_bfloat16>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up, ld_in, (__nv_bfloat16*)out, ld_out, cols, act, p0, p1);
+    if (dtype == LLME_F32) llme_launch(gated_act_kernel<float>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const float*)gate_up, ld_in, (float*)out, ld_out, cols, act, p0, p1, bias);
+    else if (dtype == LLME_BF16) llme_launch(gated_act_kernel<__nv_bfloat16>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up, ld_in, (__nv_bfloat16*)out, ld_out, cols, act, p0, p1, bias);
     else LLME_REFUSE("gated_act: unsupported dtype %d", dtype);
+    LLME_LAUNCH_STATUS();
+}
+
+LLME_API int llme_gated_act(const void* gate_up, long long ld_in, void* out, long long ld_out, int dtype, int rows, int cols, int act,
+                            float p0, float p1, cudaStream_t stream) {
+    return llme_gated_act_bias(gate_up, ld_in, out, ld_out, dtype, rows, cols, act, p0, p1, nullptr, stream);
+}
+
+// ----------------------------------------------------------------------------- out[r, :] += bias: a projection's bias behind a product without one
+template <typename T>
+__global__ void bias_add_kernel(T* __restrict__ out, long long ld, const float* __restrict__ bias, int cols) {
+    pdl_launch_dependents();
+    pdl_wait();
+    T* o = out + (size_t)blockIdx.x * ld;
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < cols; j += gridDim.y * blockDim.x) o[j] = from_f32<T>(to_f32(o[j]) + bias[j]);
+}
+
+LLME_API int llme_bias_add(void* out, long long ld, int dtype, const float* bias, int rows, int cols, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (!out || !bias) LLME_REFUSE("bias_add: null pointer");
+    const int threads = 128;
+    if (dtype == LLME_F32) llme_launch(bias_add_kernel<float>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (float*)out, ld, bias, cols);
+    else if (dtype == LLME_BF16) llme_launch(bias_add_kernel<__nv_bfloat16>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (__nv_bfloat16*)out, ld, bias, cols);
+    else LLME_REFUSE("bias_add: unsupported dtype %d", dtype);
     LLME_LAUNCH_STATUS();
 }

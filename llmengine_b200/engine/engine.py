@@ -88,6 +88,10 @@ class Engine:
                 self._caches.append(None)
                 continue
             tensor = self.cache.kv[owner] if getattr(spec, "paged", False) else self.cache.state[owner]
+            if getattr(spec, "paged", False) and getattr(spec, "state", None) is not None:
+                self._caches.append(spec.view(tensor, self.cache.run_group[i], cache_from is None,
+                                              state_tensor=self.cache.state[owner]))
+                continue
             self._caches.append(spec.view(tensor, self.cache.run_group[i], cache_from is None))
         self._init_metadata()
         self.steps = 0

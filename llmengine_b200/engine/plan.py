@@ -49,9 +49,9 @@ class Plan:
     def _add(self, kind: str, **a: Any) -> None:
         self.ops.append(Op(kind, a))
 
-    def embedding(self, table: torch.Tensor, out: torch.Tensor) -> None:
-        """out[t] = table[token_ids[t]] as 32-bit, for the step's tokens."""
-        self._add("embedding", table=table, out=out)
+    def embedding(self, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+        """out[t] = table[token_ids[t]] * scale as 32-bit, for the step's tokens."""
+        self._add("embedding", table=table, out=out, scale=float(scale))
 
     def rmsnorm(self, x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
                 delta: Optional[torch.Tensor] = None, rows: str = ROWS_TOKENS) -> None:
@@ -61,18 +61,19 @@ class Plan:
         if delta is not None:
             self.note_copy(x, None)
 
-    def linear(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], rows: str = ROWS_TOKENS) -> None:
-        """out = x w^T for the step's tokens (or its wanted rows); `out` None: the step's logits."""
-        self._add("linear", x=x, w=w, out=out, rows=rows)
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], rows: str = ROWS_TOKENS,
+               bias: Optional[torch.Tensor] = None) -> None:
+        """out = x w^T (+ bias, a 32-bit vector) for the step's tokens (or its wanted rows); `out` None: the step's logits."""
+        self._add("linear", x=x, w=w, out=out, rows=rows, bias=bias)
 
     def linear_swiglu(self, x: torch.Tensor, w_gate_up: torch.Tensor, gate_up: torch.Tensor, out: torch.Tensor,
-                      act: str = "silu", params: tuple = ()) -> None:
-        """out = act(x Wg^T, x Wu^T) with w_gate_up = [Wg | Wu] by rows; `gate_up` is the workspace of the form
+                      act: str = "silu", params: tuple = (), bias: Optional[torch.Tensor] = None) -> None:
+        """out = act(x Wg^T + bg, x Wu^T + bu) with w_gate_up = [Wg | Wu] by rows (`bias` = [bg | bu], 32-bit, or None); `gate_up` is the workspace of the form
         that runs the product and the activation as two kernels.  Gated activations of (g, u):
         "silu": g sigmoid(g) u;  "clamped_swish" with params (limit, slope): g' = min(g, limit),
         u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1)."""
         self._add("linear_swiglu", x=x, w_gate_up=w_gate_up, gate_up=gate_up, out=out, act=act,
-                  params=tuple(float(p) for p in params))
+                  params=tuple(float(p) for p in params), bias=bias)
 
     def qkv_post(self, *, q_in, k_in, v_in, num_heads: int, num_kv_heads: int, head_dim: int, q_gain=None, k_gain=None,
                  eps: float = 0.0, cos_sin=None, q_out=None, k_out=None, cache=None, group: int = 0) -> None:
@@ -105,9 +106,9 @@ class Plan:
         kernels.  Activations: "xielu" with params (a_pos, a_neg): z > 0: a_pos z^2 + z/2, else a_neg (exp(z) - 1 - z) + z/2."""
         self._add("linear_act", x=x, w=w, mid=mid, out=out, act=act, params=tuple(float(p) for p in params))
 
-    def pointwise(self, kind: str, a: torch.Tensor, b: Optional[torch.Tensor], out: torch.Tensor) -> None:
-        """Elementwise over the step's rows (row strides free).  "sigmoid_mul": out = a * sigmoid(b)."""
-        self._add("pointwise", what=kind, a=a, b=b, out=out)
+    def pointwise(self, kind: str, a: torch.Tensor, b: Optional[torch.Tensor], out: torch.Tensor, scale: float = 1.0) -> None:
+        """Elementwise over the step's rows (row strides free).  "sigmoid_mul": out = a * sigmoid(b) * scale."""
+        self._add("pointwise", what=kind, a=a, b=b, out=out, scale=float(scale))
 
     def batched_linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         """out[t, b, :] = w[b] x[t, b, :] for every batch member b (one small matrix per head): x [T, B, k] and
@@ -150,7 +151,8 @@ class Plan:
 
     def window_attention(self, *, q_in, k_in, v_in, q_gain, k_gain, eps: float, inv_freq, rot_dims: int, amplitude: float,
                          q, out, cache, group: int, num_heads: int, num_kv_heads: int, qk_dim: int, v_dim: int,
-                         window: int, keep_first: int, scale: float, sink=None, scratch=None) -> None:
+                         window: int, keep_first: int, scale: float, sink=None, scratch=None, q_bias=None, k_bias=None,
+                         v_bias=None, head_norm: bool = False) -> None:
         """Grouped-query attention over a cache whose keys are `qk_dim` and whose values are `v_dim` wide, from the raw
         projections: q_in [T, H qk_dim] and, for a layer that stores, k_in [T, G qk_dim] and v_in [T, G v_dim] (column
         ranges of one product).  With gains, queries and keys are RMS-normed over the WHOLE projection (all heads at
@@ -159,8 +161,11 @@ class Plan:
         values are stored.  Then query i sees key j if j <= i and (i - j < window or j < keep_first) (window 0: every
         earlier key); s_ij = scale (q_i . k_j); p_ij = exp(s_ij) / (sum_j' exp(s_ij') [+ exp(sink_h) with `sink` [H]]);
         out [T, H v_dim].  `q` [T, H qk_dim] is the workspace of the finished queries; `scratch` (32-bit) is where the
-        parts of single tokens meet whose keys a kernel cuts into ranges."""
-        self._add("window_attention", q_in=q_in, k_in=k_in, v_in=v_in, q_gain=q_gain, k_gain=k_gain, eps=float(eps),
+        parts of single tokens meet whose keys a kernel cuts into ranges.  Options: `q_bias`, `k_bias`, `v_bias` (32-bit
+        vectors) are added to the projections first; with `head_norm` every head is normed by itself over its qk_dim
+        coordinates and the gains are [qk_dim], shared by the heads; `v_in` may be `k_in` itself (the values are then the
+        keys as projected, before norm and rotation)."""
+        self._add("window_attention", q_bias=q_bias, k_bias=k_bias, v_bias=v_bias, head_norm=bool(head_norm), q_in=q_in, k_in=k_in, v_in=v_in, q_gain=q_gain, k_gain=k_gain, eps=float(eps),
                   inv_freq=inv_freq, rot_dims=int(rot_dims), amplitude=float(amplitude), q=q, out=out, cache=cache, group=group,
                   num_heads=num_heads, num_kv_heads=num_kv_heads, qk_dim=qk_dim, v_dim=v_dim, window=int(window),
                   keep_first=int(keep_first), scale=float(scale), sink=sink, scratch=scratch)
@@ -188,3 +193,30 @@ class Plan:
         """out[t] = base[t] (if given) + sum_k weights[t, k] * y[t * top_k + k], the choices added in their order,
         in 32-bit."""
         self._add("moe_combine", y=y, weights=weights, base=base, out=out)
+
+    def short_conv(self, *, x, w, bias, state, out, act: Optional[str] = "silu") -> None:
+        """Causal convolution per channel over each request's tokens: y_t = bias + sum_j w[:, K-1-j] x_(t-j) with zeros
+        before the request's start, then `act` ("silu" or None).  x [T, C] (any row stride), w [C, K] and bias [C] 32-bit,
+        out [T, C] 32-bit.  `state` [slots, K - 1, C] 32-bit holds each request's last K - 1 inputs between steps."""
+        self._add("short_conv", x=x, w=w, bias=bias, state=state, out=out, act=act)
+
+    def rotate(self, *, x, out, heads, scale, dim: int, rot_dims: int, inv_freq) -> None:
+        """Rotation by position into 32-bit: for each of up to two tensors x[i] [T, heads[i] * dim] the first `rot_dims`
+        coordinates of every head turn in rotate-half pairs by position * inv_freq[j]; the rest pass; then times scale[i]."""
+        self._add("rotate", x=tuple(x), out=tuple(out), heads=tuple(heads), scale=tuple(scale), dim=int(dim), rot_dims=int(rot_dims),
+                  inv_freq=inv_freq)
+
+    def recurrence(self, *, q, k, v, state, out, heads: int, n: int, p: int, qk_groups: int, decay=None, dt=None, dt_bias=None,
+                   a_log=None, skip=None) -> None:
+        """Per request and head, over the request's tokens in order: S_t = a_t S_(t-1) + s_t k_t v_t^T (S is n x p),
+        y_t = S_t^T q_t + skip_h v_t.  With `decay` [H]: a_t = decay_h, s_t = 1.  With `dt` [T, H], `dt_bias` and `a_log`
+        [H]: d = softplus(dt + dt_bias), a_t = exp(-exp(a_log_h) d), s_t = d.  q, k [T, qk_groups * n] and out [T, H p] are
+        32-bit; head h reads group h // (H / qk_groups).  `state` [slots, H, p, n] 32-bit goes from step to step."""
+        self._add("recurrence", q=q, k=k, v=v, state=state, out=out, heads=int(heads), n=int(n), p=int(p), qk_groups=int(qk_groups),
+                  decay=decay, dt=dt, dt_bias=dt_bias, a_log=a_log, skip=skip)
+
+    def gated_norm(self, *, y, gate, weight, out, group: int, gate_first: bool, eps: float, scale: float = 1.0) -> None:
+        """RMS norm of y [T, C] (32-bit) in groups of `group` columns, with g = silu(gate): `gate_first`: u = y g,
+        out = u / rms(u) * weight; else out = y / rms(y) * weight * g; then times `scale`.  `weight` [C] 32-bit or None."""
+        self._add("gated_norm", y=y, gate=gate, weight=weight, out=out, group=int(group), gate_first=bool(gate_first),
+                  eps=float(eps), scale=float(scale))

@@ -69,7 +69,7 @@ enum LlmeOpKind {
     LLME_OP_EMBEDDING = 1, LLME_OP_RMSNORM, LLME_OP_LINEAR, LLME_OP_LINEAR_SWIGLU, LLME_OP_QKV_POST, LLME_OP_ATTEND,
     LLME_OP_ATTENTION, LLME_OP_CALL, LLME_OP_LINEAR_ACT, LLME_OP_POINTWISE, LLME_OP_BATCHED_LINEAR, LLME_OP_RESIDUAL_ADD,
     LLME_OP_LATENT_ATTENTION, LLME_OP_TOKEN_SIDE, LLME_OP_POSTNORM, LLME_OP_WINDOW_ATTENTION, LLME_OP_MOE_ROUTE,
-    LLME_OP_GROUPED_LINEAR, LLME_OP_MOE_COMBINE
+    LLME_OP_GROUPED_LINEAR, LLME_OP_MOE_COMBINE, LLME_OP_SHORT_CONV, LLME_OP_ROTATE, LLME_OP_RECURRENCE, LLME_OP_GATED_NORM
 };
 
 enum { LLME_ACT_XIELU = 1 };
@@ -83,6 +83,7 @@ enum { LLME_ROWS_TOKENS = 0, LLME_ROWS_LOGITS = 1 };
 typedef struct LlmeEmbeddingOp {
     const void* table; int table_dtype, vocab, hidden;
     float* out;                /* [T, hidden] */
+    float scale;               /* every row times this constant, in 32-bit (1: none) */
 } LlmeEmbeddingOp;
 
 typedef struct LlmeRmsNormOp {
@@ -100,6 +101,7 @@ typedef struct LlmeLinearOp {
     void* out; long long ldo; int out_dtype;   /* out NULL: the step's logits, row stride n */
     int n, k;
     int rows;                  /* LLME_ROWS_TOKENS or LLME_ROWS_LOGITS */
+    const float* bias;         /* [n] added to every row of the product, or NULL */
 } LlmeLinearOp;
 
 typedef struct LlmeLinearSwigluOp {
@@ -109,6 +111,7 @@ typedef struct LlmeLinearSwigluOp {
     void* out; long long ldo;  /* [T, inter] */
     int inter, k;
     int act; float p0, p1;     /* LLME_GATE_* and its constants */
+    const float* bias;         /* [2 * inter] biases of the gate and up rows, added before the activation, or NULL */
 } LlmeLinearSwigluOp;
 
 /* QK norm, rotation and cache write as a step of its own (the parts of it that are given). */
@@ -147,12 +150,13 @@ typedef struct LlmeLinearActOp {
     int act; float p0, p1;
 } LlmeLinearActOp;
 
-/* Elementwise over the step's rows.  LLME_POINTWISE_SIGMOID_MUL: out = a * sigmoid(b). */
+/* Elementwise over the step's rows.  LLME_POINTWISE_SIGMOID_MUL: out = a * sigmoid(b) * scale. */
 typedef struct LlmePointwiseOp {
     int what, dtype, cols;
     const void* a; long long lda;
     const void* b; long long ldb;
     void* out; long long ldo;
+    float scale;
 } LlmePointwiseOp;
 
 /* out[t, b, :] = w[b] x[t, b, :] for b < batch: one small matrix per member (a head). */
@@ -214,6 +218,9 @@ typedef struct LlmeWindowAttentionOp {
     int nh, nkv, dk, dv, window, keep_first; float scale;
     const float* sink;
     float* scratch; long long scratch_floats;                /* for single tokens whose keys are cut into ranges, or NULL */
+    /* options (off when zero): biases of the projections, added first; head_norm 1: every head is normed by itself and the
+     * gains are [dk], shared by the heads.  v_in may be k_in itself: the values are then the keys as projected. */
+    const float* q_bias; const float* k_bias; const float* v_bias; int head_norm;
 } LlmeWindowAttentionOp;
 
 /* Routing of a mixture of experts: s = sigmoid(logits), the top_k largest, w_e = scale * s_e / (sum of the chosen s + 1e-20);
@@ -237,6 +244,50 @@ typedef struct LlmeGroupedLinearOp {
 typedef struct LlmeMoeCombineOp {
     const float* y; long long ldy; const float* weights; const float* base; float* out; int top_k, size;
 } LlmeMoeCombineOp;
+
+/* Causal convolution per channel over each request's tokens, y_t = bias + sum_j w[:, K-1-j] x_(t-j), then silu (act 1);
+ * the request's last K - 1 inputs live in its state slot ([K - 1, channels] 32-bit, zero when the request starts). */
+typedef struct LlmeShortConvOp {
+    const void* x; long long ldx; int x_dtype;
+    const float* w; const float* bias;
+    float* state; long long state_stride;
+    float* out; long long ldo;
+    int channels, taps, act;
+} LlmeShortConvOp;
+
+/* Rotation of the first rot_dims coordinates of every head of up to two tensors by the tokens' positions (rotate-half
+ * pairs, angle position * inv_freq[i]), each then times a constant; results in 32-bit. */
+typedef struct LlmeRotateOp {
+    const void* x[2]; long long ldx[2]; float* out[2]; long long ldo[2]; int heads[2]; float scale[2];
+    int dtype, dim, rot_dims;
+    const float* inv_freq;
+} LlmeRotateOp;
+
+/* Linear recurrence with a matrix state per head and request: S_t = a_t S_(t-1) + s_t k_t v_t^T, y_t = S_t^T q_t + skip_h v_t
+ * (csrc/recurrent.cu).  gate 0: a_t = decay[h], s_t = 1; gate 1: d = softplus(dt[t, h] + dt_bias[h]), a_t = exp(-exp(a_log[h]) d),
+ * s_t = d.  State [heads, p, n] 32-bit per slot, zero when the request starts. */
+typedef struct LlmeRecurrenceOp {
+    const float* q; const float* k; long long ldq, ldk; int qk_groups;
+    const void* v; long long ldv; int v_dtype;
+    int gate;
+    const float* decay;
+    const void* dt; long long lddt; int dt_dtype; const float* dt_bias; const float* a_log;
+    const float* skip;
+    float* state; long long state_stride;
+    float* out; long long ldo;
+    int heads, n, p;
+} LlmeRecurrenceOp;
+
+/* RMS norm in groups of `group` columns with a silu gate: gate_first 1: u = y silu(g), out = u / rms(u) * weight; 0:
+ * out = y / rms(y) * weight * silu(g); then times `scale`. */
+typedef struct LlmeGatedNormOp {
+    const float* y; long long ldy;
+    const void* gate; long long ldg;
+    const float* weight;
+    void* out; long long ldo;
+    int dtype, cols, group, gate_first;
+    float eps, scale;
+} LlmeGatedNormOp;
 
 typedef struct LlmeExecutor LlmeExecutor;
 typedef struct LlmePlan LlmePlan;
@@ -334,6 +385,10 @@ public:
     int add(const LlmeMoeRouteOp& r) { return add(LLME_OP_MOE_ROUTE, &r, sizeof r); }
     int add(const LlmeGroupedLinearOp& r) { return add(LLME_OP_GROUPED_LINEAR, &r, sizeof r); }
     int add(const LlmeMoeCombineOp& r) { return add(LLME_OP_MOE_COMBINE, &r, sizeof r); }
+    int add(const LlmeShortConvOp& r) { return add(LLME_OP_SHORT_CONV, &r, sizeof r); }
+    int add(const LlmeRotateOp& r) { return add(LLME_OP_ROTATE, &r, sizeof r); }
+    int add(const LlmeRecurrenceOp& r) { return add(LLME_OP_RECURRENCE, &r, sizeof r); }
+    int add(const LlmeGatedNormOp& r) { return add(LLME_OP_GATED_NORM, &r, sizeof r); }
     /* One step through the whole plan; throws with the failing record's message. */
     void run(const LlmeStep& step, cudaStream_t stream) {
         if (llme_plan_run(h_, &step, 0, -1, stream)) throw std::runtime_error(ex_.error());

@@ -37,6 +37,8 @@ SOURCES: Dict[str, str] = {
     # the same on the tensor cores, per pair of sizes: "attention_window_tc@DK=64,DV=64"
     "attention_window_tc": "attention_window_tc.cu",
     # mixture of experts: routing, the grouped product (plain form), the weighted sum; and the grouped product on tensor cores
+    # layers with a state of fixed size per request: short convolution, linear recurrence, gated group norm
+    "recurrent": "recurrent.cu",
     "moe": "moe.cu",
     "moe_tc": "moe_tc.cu",
     "gemm_f32": "gemm_f32.cu",

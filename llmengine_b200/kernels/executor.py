@@ -13,7 +13,7 @@ F32, BF16 = 0, 1
 ROWS = {"tokens": 0, "logits": 1}
 (OP_EMBEDDING, OP_RMSNORM, OP_LINEAR, OP_LINEAR_SWIGLU, OP_QKV_POST, OP_ATTEND, OP_ATTENTION, OP_CALL, OP_LINEAR_ACT,
  OP_POINTWISE, OP_BATCHED_LINEAR, OP_RESIDUAL_ADD, OP_LATENT_ATTENTION, OP_TOKEN_SIDE, OP_POSTNORM, OP_WINDOW_ATTENTION,
- OP_MOE_ROUTE, OP_GROUPED_LINEAR, OP_MOE_COMBINE) = range(1, 20)
+ OP_MOE_ROUTE, OP_GROUPED_LINEAR, OP_MOE_COMBINE, OP_SHORT_CONV, OP_ROTATE, OP_RECURRENCE, OP_GATED_NORM) = range(1, 24)
 GATES = {"silu": 0, "clamped_swish": 1}
 ACTIVATIONS = {"xielu": 1}
 POINTWISE = {"sigmoid_mul": 1}
@@ -51,7 +51,8 @@ CallFn = CFUNCTYPE(c_int, c_void_p, POINTER(Step), c_void_p)
 
 
 class EmbeddingOp(Structure):
-    _fields_ = [("table", c_void_p), ("table_dtype", c_int), ("vocab", c_int), ("hidden", c_int), ("out", c_void_p)]
+    _fields_ = [("table", c_void_p), ("table_dtype", c_int), ("vocab", c_int), ("hidden", c_int), ("out", c_void_p),
+                ("scale", c_float)]
 
 
 class RmsNormOp(Structure):
@@ -62,13 +63,13 @@ class RmsNormOp(Structure):
 class LinearOp(Structure):
     _fields_ = [("x", c_void_p), ("ldx", c_longlong), ("x_dtype", c_int), ("w", c_void_p), ("ldw", c_longlong),
                 ("w_dtype", c_int), ("out", c_void_p), ("ldo", c_longlong), ("out_dtype", c_int), ("n", c_int), ("k", c_int),
-                ("rows", c_int)]
+                ("rows", c_int), ("bias", c_void_p)]
 
 
 class LinearSwigluOp(Structure):
     _fields_ = [("x", c_void_p), ("ldx", c_longlong), ("dtype", c_int), ("w_gate_up", c_void_p), ("ldw", c_longlong),
                 ("gate_up", c_void_p), ("out", c_void_p), ("ldo", c_longlong), ("inter", c_int), ("k", c_int),
-                ("act", c_int), ("p0", c_float), ("p1", c_float)]
+                ("act", c_int), ("p0", c_float), ("p1", c_float), ("bias", c_void_p)]
 
 
 class QkvPostOp(Structure):
@@ -98,7 +99,7 @@ class LinearActOp(Structure):
 
 class PointwiseOp(Structure):
     _fields_ = [("what", c_int), ("dtype", c_int), ("cols", c_int), ("a", c_void_p), ("lda", c_longlong), ("b", c_void_p),
-                ("ldb", c_longlong), ("out", c_void_p), ("ldo", c_longlong)]
+                ("ldb", c_longlong), ("out", c_void_p), ("ldo", c_longlong), ("scale", c_float)]
 
 
 class BatchedLinearOp(Structure):
@@ -138,7 +139,8 @@ class WindowAttentionOp(Structure):
                 ("inv_freq", c_void_p), ("rot_dims", c_int), ("amplitude", c_float), ("q", c_void_p), ("out", c_void_p),
                 ("cache", c_void_p), ("group", c_int), ("nh", c_int), ("nkv", c_int), ("dk", c_int), ("dv", c_int),
                 ("window", c_int), ("keep_first", c_int), ("scale", c_float), ("sink", c_void_p), ("scratch", c_void_p),
-                ("scratch_floats", c_longlong)]
+                ("scratch_floats", c_longlong), ("q_bias", c_void_p), ("k_bias", c_void_p), ("v_bias", c_void_p),
+                ("head_norm", c_int)]
 
 
 class MoeRouteOp(Structure):
@@ -156,6 +158,40 @@ class GroupedLinearOp(Structure):
 class MoeCombineOp(Structure):
     _fields_ = [("y", c_void_p), ("ldy", c_longlong), ("weights", c_void_p), ("base", c_void_p), ("out", c_void_p),
                 ("top_k", c_int), ("size", c_int)]
+
+
+class ShortConvOp(Structure):
+    _fields_ = [("x", c_void_p), ("ldx", c_longlong), ("x_dtype", c_int), ("w", c_void_p), ("bias", c_void_p),
+                ("state", c_void_p), ("state_stride", c_longlong), ("out", c_void_p), ("ldo", c_longlong),
+                ("channels", c_int), ("taps", c_int), ("act", c_int)]
+
+
+class RotateOp(Structure):
+    _fields_ = [("x", c_void_p * 2), ("ldx", c_longlong * 2), ("out", c_void_p * 2), ("ldo", c_longlong * 2), ("heads", c_int * 2),
+                ("scale", c_float * 2), ("dtype", c_int), ("dim", c_int), ("rot_dims", c_int), ("inv_freq", c_void_p)]
+
+
+class RecurrenceOp(Structure):
+    _fields_ = [("q", c_void_p), ("k", c_void_p), ("ldq", c_longlong), ("ldk", c_longlong), ("qk_groups", c_int),
+                ("v", c_void_p), ("ldv", c_longlong), ("v_dtype", c_int), ("gate", c_int), ("decay", c_void_p),
+                ("dt", c_void_p), ("lddt", c_longlong), ("dt_dtype", c_int), ("dt_bias", c_void_p), ("a_log", c_void_p),
+                ("skip", c_void_p), ("state", c_void_p), ("state_stride", c_longlong), ("out", c_void_p), ("ldo", c_longlong),
+                ("heads", c_int), ("n", c_int), ("p", c_int)]
+
+
+class GatedNormOp(Structure):
+    _fields_ = [("y", c_void_p), ("ldy", c_longlong), ("gate", c_void_p), ("ldg", c_longlong), ("weight", c_void_p),
+                ("out", c_void_p), ("ldo", c_longlong), ("dtype", c_int), ("cols", c_int), ("group", c_int),
+                ("gate_first", c_int), ("eps", c_float), ("scale", c_float)]
+
+
+def _f32(t, n=None) -> bool:
+    return t is None or (t.dtype == torch.float32 and t.is_contiguous() and (n is None or t.numel() == n))
+
+
+def _state(t) -> bool:
+    """A 32-bit state [slots, ...]: every slot's part is dense; the slots may lie apart (several states share a row)."""
+    return t.dtype == torch.float32 and t[0].is_contiguous()
 
 
 def declare(lib: ctypes.CDLL) -> None:
@@ -223,7 +259,7 @@ def records(op, keep: List[Any]):
     if k == "embedding":
         t, out = a["table"], a["out"]
         assert out.dtype == torch.float32 and t.is_contiguous() and out.is_contiguous()
-        return OP_EMBEDDING, EmbeddingOp(t.data_ptr(), code(t.dtype), t.shape[0], t.shape[1], out.data_ptr())
+        return OP_EMBEDDING, EmbeddingOp(t.data_ptr(), code(t.dtype), t.shape[0], t.shape[1], out.data_ptr(), float(a.get("scale", 1.0)))
     if k == "rmsnorm":
         x, d, g, out = a["x"], a["delta"], a["gain"], a["out"]
         assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and (d is None or d.is_contiguous())
@@ -233,17 +269,19 @@ def records(op, keep: List[Any]):
         x, w, out = a["x"], a["w"], a["out"]
         assert x.stride(1) == 1 and w.stride(1) == 1 and w.shape[1] == x.shape[1] and (out is None or out.stride(1) == 1)
         assert out is None or out.shape[1] == w.shape[0]
+        assert _f32(a.get("bias"), w.shape[0])
         return OP_LINEAR, LinearOp(x.data_ptr(), x.stride(0), code(x.dtype), w.data_ptr(), w.stride(0), code(w.dtype), ptr(out),
                                    out.stride(0) if out is not None else 0, code(out.dtype) if out is not None else F32,
-                                   w.shape[0], w.shape[1], ROWS[a["rows"]])
+                                   w.shape[0], w.shape[1], ROWS[a["rows"]], ptr(a.get("bias")))
     if k == "linear_swiglu":
         x, w, gu, out = a["x"], a["w_gate_up"], a["gate_up"], a["out"]
         assert x.dtype == w.dtype == out.dtype and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
         assert w.shape[0] == 2 * out.shape[1] and w.shape[1] == x.shape[1]
         p = a.get("params", ())
+        assert _f32(a.get("bias"), w.shape[0])
         return OP_LINEAR_SWIGLU, LinearSwigluOp(x.data_ptr(), x.stride(0), code(x.dtype), w.data_ptr(), w.stride(0), ptr(gu),
                                                 out.data_ptr(), out.stride(0), out.shape[1], x.shape[1], GATES[a.get("act", "silu")],
-                                                p[0] if p else 0.0, p[1] if len(p) > 1 else 0.0)
+                                                p[0] if p else 0.0, p[1] if len(p) > 1 else 0.0, ptr(a.get("bias")))
     if k == "qkv_post":
         return OP_QKV_POST, _qkv_post_record(a)
     if k == "attend":
@@ -273,7 +311,7 @@ def records(op, keep: List[Any]):
         x, b, out = a["a"], a["b"], a["out"]
         assert x.stride(1) == 1 and out.stride(1) == 1 and (b is None or (b.stride(1) == 1 and b.dtype == x.dtype)) and out.dtype == x.dtype
         return OP_POINTWISE, PointwiseOp(POINTWISE[a["what"]], code(x.dtype), out.shape[1], x.data_ptr(), x.stride(0), ptr(b),
-                                         b.stride(0) if b is not None else 0, out.data_ptr(), out.stride(0))
+                                         b.stride(0) if b is not None else 0, out.data_ptr(), out.stride(0), float(a.get("scale", 1.0)))
     if k == "batched_linear":
         x, w, out = a["x"], a["w"], a["out"]
         assert x.dim() == 3 and w.dim() == 3 and out.dim() == 3 and x.stride(2) == 1 and out.stride(2) == 1 and w.is_contiguous()
@@ -325,13 +363,16 @@ def records(op, keep: List[Any]):
         assert cache.is_contiguous() and qi.shape[1] == q.shape[1] == H * dk and out.shape[1] == H * dv and cache.shape[1] % (G * (dk + dv)) == 0
         assert (ki is None) == (vi is None) and (ki is None or (ki.dtype == vi.dtype == qi.dtype and ki.stride(1) == vi.stride(1) == 1
                                                               and ki.shape[1] == G * dk and vi.shape[1] == G * dv))
-        for t, n in ((a["q_gain"], H * dk), (a["k_gain"], G * dk), (a["sink"], H), (a["inv_freq"], a["rot_dims"] // 2)):
+        per_head = bool(a.get("head_norm"))
+        for t, n in ((a["q_gain"], dk if per_head else H * dk), (a["k_gain"], dk if per_head else G * dk), (a["sink"], H),
+                     (a["inv_freq"], a["rot_dims"] // 2), (a.get("q_bias"), H * dk), (a.get("k_bias"), G * dk), (a.get("v_bias"), G * dv)):
             assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n)
         return OP_WINDOW_ATTENTION, WindowAttentionOp(
             qi.data_ptr(), ptr(ki), ptr(vi), qi.stride(0), ki.stride(0) if ki is not None else 0, vi.stride(0) if vi is not None else 0,
             code(qi.dtype), ptr(a["q_gain"]), ptr(a["k_gain"]), a["eps"], ptr(a["inv_freq"]), a["rot_dims"], a["amplitude"],
             q.data_ptr(), out.data_ptr(), cache.data_ptr(), a["group"], H, G, dk, dv, a["window"], a["keep_first"], a["scale"],
-            ptr(a["sink"]), ptr(a.get("scratch")), a["scratch"].numel() if a.get("scratch") is not None else 0)
+            ptr(a["sink"]), ptr(a.get("scratch")), a["scratch"].numel() if a.get("scratch") is not None else 0,
+            ptr(a.get("q_bias")), ptr(a.get("k_bias")), ptr(a.get("v_bias")), 1 if a.get("head_norm") else 0)
     if k == "moe_route":
         z, ex_, wt, off, order, counts = a["logits"], a["experts"], a["weights"], a["offsets"], a["order"], a["counts"]
         assert z.dtype == wt.dtype == torch.float32 and z.stride(1) == 1 and ex_.is_contiguous() and wt.is_contiguous()
@@ -354,4 +395,44 @@ def records(op, keep: List[Any]):
         assert y.dtype == wt.dtype == out.dtype == torch.float32 and y.stride(1) == 1 and wt.is_contiguous() and out.is_contiguous()
         assert base is None or (base.dtype == torch.float32 and base.is_contiguous() and base.shape[1] == out.shape[1])
         return OP_MOE_COMBINE, MoeCombineOp(y.data_ptr(), y.stride(0), wt.data_ptr(), ptr(base), out.data_ptr(), wt.shape[1], out.shape[1])
+    if k == "short_conv":
+        x, w, b, st, out = a["x"], a["w"], a["bias"], a["state"], a["out"]
+        C, K = w.shape
+        assert x.stride(1) == 1 and x.shape[1] == C and out.dtype == torch.float32 and out.stride(1) == 1 and out.shape[1] == C
+        assert _f32(w) and _f32(b, C) and _state(st) and st.dim() == 3 and tuple(st.shape[1:]) == (max(K - 1, 1), C)
+        return OP_SHORT_CONV, ShortConvOp(x.data_ptr(), x.stride(0), code(x.dtype), w.data_ptr(), ptr(b), st.data_ptr(), st.stride(0),
+                                          out.data_ptr(), out.stride(0), C, K, 1 if a["act"] == "silu" else 0)
+    if k == "rotate":
+        xs, outs, heads, scales = a["x"], a["out"], a["heads"], a["scale"]
+        ref = next(t for t in xs if t is not None)
+        for t, o, h in zip(xs, outs, heads):
+            assert t is None or (t.dtype == ref.dtype and t.stride(1) == 1 and o.dtype == torch.float32 and o.stride(1) == 1
+                                 and t.shape[1] == o.shape[1] == h * a["dim"])
+        assert _f32(a["inv_freq"], a["rot_dims"] // 2)
+        A = lambda ty, v: (ty * 2)(*v)
+        return OP_ROTATE, RotateOp(A(c_void_p, [ptr(t) for t in xs]), A(c_longlong, [t.stride(0) if t is not None else 0 for t in xs]),
+                                   A(c_void_p, [ptr(t) for t in outs]), A(c_longlong, [t.stride(0) if t is not None else 0 for t in outs]),
+                                   A(c_int, [int(h) for h in heads]), A(c_float, [float(v) for v in scales]), code(ref.dtype),
+                                   a["dim"], a["rot_dims"], ptr(a["inv_freq"]))
+    if k == "recurrence":
+        q, kk, v, st, out = a["q"], a["k"], a["v"], a["state"], a["out"]
+        H, n, p, G = a["heads"], a["n"], a["p"], a["qk_groups"]
+        assert q.dtype == kk.dtype == out.dtype == torch.float32 and q.stride(1) == kk.stride(1) == v.stride(1) == out.stride(1) == 1
+        assert q.shape[1] == kk.shape[1] == G * n and v.shape[1] == out.shape[1] == H * p and H % G == 0
+        assert _state(st) and tuple(st.shape[1:]) == (H, p, n)
+        dt = a.get("dt")
+        assert dt is None or (dt.stride(1) == 1 and dt.shape[1] == H)
+        for t in ("decay", "dt_bias", "a_log", "skip"):
+            assert _f32(a.get(t), H)
+        return OP_RECURRENCE, RecurrenceOp(q.data_ptr(), kk.data_ptr(), q.stride(0), kk.stride(0), G, v.data_ptr(), v.stride(0), code(v.dtype),
+                                           0 if dt is None else 1, ptr(a.get("decay")), ptr(dt), dt.stride(0) if dt is not None else 0,
+                                           code(dt.dtype) if dt is not None else 0, ptr(a.get("dt_bias")), ptr(a.get("a_log")),
+                                           ptr(a.get("skip")), st.data_ptr(), st.stride(0), out.data_ptr(), out.stride(0), H, n, p)
+    if k == "gated_norm":
+        y, g, w, out = a["y"], a["gate"], a["weight"], a["out"]
+        cols = y.shape[1]
+        assert y.dtype == torch.float32 and y.stride(1) == g.stride(1) == out.stride(1) == 1 and g.dtype == out.dtype
+        assert g.shape[1] == out.shape[1] == cols and cols % a["group"] == 0 and _f32(w, cols)
+        return OP_GATED_NORM, GatedNormOp(y.data_ptr(), y.stride(0), g.data_ptr(), g.stride(0), ptr(w), out.data_ptr(), out.stride(0),
+                                          code(out.dtype), cols, a["group"], 1 if a["gate_first"] else 0, a["eps"], a["scale"])
     raise ValueError(f"the executor has no record for the operation {k!r}")

@@ -192,11 +192,15 @@ class CudaOps:
 
     _ENTRY_POINTS = {
         "elementwise": {"embedding": "llme_embedding", "rmsnorm": "llme_rmsnorm", "qkv_post": "llme_qkv_post",
-                        "swiglu": "llme_swiglu"},
+                        "swiglu": "llme_swiglu", "embedding_scaled": "llme_embedding_scaled"},
         "gemm_f32": {"gemm_f32": "llme_gemm_nt_f32", "gemm_f32_batched": "llme_gemm_nt_f32_batched"},
         "pointwise": {"xielu": "llme_xielu", "sigmoid_mul": "llme_sigmoid_mul", "residual_add": "llme_residual_add",
                       "gelu_gather_mul": "llme_gelu_gather_mul", "rmsnorm_add": "llme_rmsnorm_add",
-                      "latent_post": "llme_latent_post", "postnorm": "llme_postnorm", "gated_act": "llme_gated_act"},
+                      "latent_post": "llme_latent_post", "postnorm": "llme_postnorm", "gated_act": "llme_gated_act",
+                      "sigmoid_mul_scaled": "llme_sigmoid_mul_scaled", "gated_act_bias": "llme_gated_act_bias",
+                      "bias_add": "llme_bias_add"},
+        "recurrent": {"short_conv": "llme_short_conv", "rotate": "llme_rotate", "recurrence": "llme_recurrence",
+                      "gated_norm": "llme_gated_norm"},
         "attention_window": {"window_post": "llme_window_post", "window_attention_plain": "llme_window_attention_plain"},
         "attention_window_tc": {"window_attention_tc/{hd}": "llme_window_attention_tc"},
         "moe": {"moe_route": "llme_moe_route", "grouped_linear": "llme_grouped_linear", "moe_combine": "llme_moe_combine"},
@@ -241,8 +245,12 @@ class CudaOps:
                 want("elementwise")
             if op.kind in ("linear_act", "pointwise", "residual_add", "latent_attention", "token_side", "postnorm"):
                 want("pointwise")
-            if op.kind == "linear_swiglu" and a.get("act", "silu") != "silu":
+            if op.kind == "linear_swiglu" and (a.get("act", "silu") != "silu" or a.get("bias") is not None):
                 want("pointwise")
+            if op.kind == "linear" and a.get("bias") is not None:
+                want("pointwise")
+            if op.kind in ("short_conv", "rotate", "recurrence", "gated_norm"):
+                want("recurrent")
             if op.kind == "window_attention":
                 want("attention_window")
                 if fast_attention and build.has_source("attention_window_tc") and self.window_tc_supports(a["qk_dim"], a["v_dim"], a["q"].dtype):

@@ -158,12 +158,25 @@ class WindowSinkAttention(Part):
       names (keys as stored there, normed and rotated); `retain_window` / `retain_first` then say what that cache
       keeps (the widest needs among the layers that read it), which may be more than this layer's own mask.
 
-    Tensors: q, k, v, o; q.norm, k.norm; sink."""
+    * `head_norm`: the norm of q and k is taken per head over its qk_dim coordinates, with gain vectors of that size
+      shared by the heads, instead of over the whole projection;
+    * `biases`: the q and k projections (and v, where there is one) have biases (<tensor>.b), added in the projection;
+    * `values_are_keys`: there is no value projection; a token's values are its keys as projected (with the bias,
+      before norm and rotation), so v_dim = qk_dim;
+    * `gate` "sigmoid": the concatenated heads are multiplied by sigmoid(W_g h) (tensor g) before the output product;
+      W_g reads the same input as the other projections and is stored with them as one matrix.
+
+    Tensors: q, k, v, o; q.norm, k.norm; sink; g; q.b, k.b, v.b.
+
+    Beside `emit` the part has the pieces a mixer of several branches puts together itself: `w_in` (all projections of the
+    input as one matrix), `emit_heads` (from that product to the gated heads, times a constant, into a place of the
+    caller's) and `w_o`."""
 
     def __init__(self, rt: Runtime, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, qk_dim: int,
                  v_dim: int, scale: float, norm_eps: Optional[float] = None, position_encoding: Optional[PartSpec] = None,
                  window: int = 0, keep_first: int = 0, sink: bool = False, own_kv: bool = True,
-                 retain_window: Optional[int] = None, retain_first: Optional[int] = None):
+                 retain_window: Optional[int] = None, retain_first: Optional[int] = None, head_norm: bool = False,
+                 biases: bool = False, values_are_keys: bool = False, gate: Optional[str] = None):
         super().__init__(rt, prefix)
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
@@ -176,59 +189,106 @@ class WindowSinkAttention(Part):
         if self.retain_window and (not self.window or self.window > self.retain_window or self.keep_first > self.retain_first):
             raise ValueError(f"{prefix}: the cache keeps less than the layer's mask needs")
         self.has_sink, self.own_kv = bool(sink), bool(own_kv)
+        self.head_norm, self.biases, self.values_are_keys = bool(head_norm), bool(biases), bool(values_are_keys)
+        if gate not in (None, "sigmoid"):
+            raise ValueError(f"{prefix}: unknown output gate {gate!r}; known: sigmoid")
+        self.gate = gate
+        if self.values_are_keys and self.dv != self.dk:
+            raise ValueError(f"{prefix}: values that are the keys have the keys' size, not {self.dv} against {self.dk}")
+        if self.values_are_keys and not self.own_kv:
+            raise ValueError(f"{prefix}: values_are_keys describes a layer with a key projection of its own")
         self.position = build_part("position", position_encoding, rt, prefix) if position_encoding is not None else None
         if self.position is not None and self.position.dims > self.dk:
             raise ValueError(f"{prefix}: {self.position.dims} rotated coordinates do not fit a head of {self.dk}")
         self.q_size, self.k_size, self.v_size = self.nh * self.dk, self.nkv * self.dk, self.nkv * self.dv
         self.o_size = self.nh * self.dv
+        self.heads_size = self.o_size
+        self.has_v = self.own_kv and not self.values_are_keys
         self.w_in = self.w_o = self.q_gain = self.k_gain = self.sink = None
+        self.q_bias = self.k_bias = self.v_bias = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         s = {self.name("q"): WeightSpec((self.q_size, self.hidden)), self.name("o"): WeightSpec((self.hidden, self.o_size))}
         if self.own_kv:
             s[self.name("k")] = WeightSpec((self.k_size, self.hidden))
+        if self.has_v:
             s[self.name("v")] = WeightSpec((self.v_size, self.hidden))
+        if self.gate is not None:
+            s[self.name("g")] = WeightSpec((self.o_size, self.hidden))
         if self.eps is not None:
-            s[self.name("q.norm")] = WeightSpec((self.q_size,), role="vector", init="gain")
+            s[self.name("q.norm")] = WeightSpec((self.dk if self.head_norm else self.q_size,), role="vector", init="gain")
             if self.own_kv:
-                s[self.name("k.norm")] = WeightSpec((self.k_size,), role="vector", init="gain")
+                s[self.name("k.norm")] = WeightSpec((self.dk if self.head_norm else self.k_size,), role="vector", init="gain")
         if self.has_sink:
             s[self.name("sink")] = WeightSpec((self.nh,), role="vector", init="unit")
+        if self.biases:
+            s[self.name("q.b")] = WeightSpec((self.q_size,), role="vector")
+            if self.own_kv:
+                s[self.name("k.b")] = WeightSpec((self.k_size,), role="vector")
+            if self.has_v:
+                s[self.name("v.b")] = WeightSpec((self.v_size,), role="vector")
         return s
 
     def load_weights(self, t: Dict[str, torch.Tensor]) -> None:
-        parts = [t[self.name("q")]] + ([t[self.name("k")], t[self.name("v")]] if self.own_kv else [])
+        parts = [t[self.name("q")]] + ([t[self.name("k")]] if self.own_kv else []) + ([t[self.name("v")]] if self.has_v else [])
+        if self.gate is not None:
+            parts.append(t[self.name("g")])
         self.w_in = torch.cat(parts, dim=0).contiguous()
         self.w_o = t[self.name("o")].contiguous()
         if self.eps is not None:
             self.q_gain = t[self.name("q.norm")].float().contiguous()
             self.k_gain = t[self.name("k.norm")].float().contiguous() if self.own_kv else None
         self.sink = t[self.name("sink")].float().contiguous() if self.has_sink else None
+        if self.biases:
+            self.q_bias = t[self.name("q.b")].float().contiguous()
+            self.k_bias = t[self.name("k.b")].float().contiguous() if self.own_kv else None
+            self.v_bias = t[self.name("v.b")].float().contiguous() if self.has_v else (self.k_bias if self.values_are_keys else None)
+
+    @property
+    def in_size(self) -> int:
+        """Rows of `w_in`: the width of the product that holds every projection of the mixer's input."""
+        return self.q_size + (self.k_size if self.own_kv else 0) + (self.v_size if self.has_v else 0) + (self.o_size if self.gate else 0)
 
     def cache_spec(self) -> SplitKVSpec:
         return SplitKVSpec(self.nkv, self.dk, self.dv, self.retain_window, self.retain_first)
 
-    def emit(self, plan: Plan, h: torch.Tensor, cache) -> torch.Tensor:
+    def emit_heads(self, plan: Plan, proj: torch.Tensor, cache, out: torch.Tensor, scale: float = 1.0) -> None:
+        """From `proj` = h w_in^T [T, in_size] to the heads [T, num_heads v_dim] (gated, where the layer has a gate), times
+        `scale`, written to `out` (any row stride)."""
         rt = self.rt
         if cache.writes != self.own_kv:
             raise ValueError(f"{self.prefix}: a layer with key and value projections keeps a cache of its own, one "
                              f"without reads another layer's")
         qs, ks = self.q_size, self.k_size
-        proj = rt.workspace("qkv", self.w_in.shape[0], rt.dtype)
-        plan.linear(h, self.w_in, proj)
         q = rt.workspace("q", qs, rt.dtype)
-        out = rt.workspace("attn_out", self.o_size, rt.dtype)
+        k_in = proj[:, qs:qs + ks] if self.own_kv else None
+        v_in = (k_in if self.values_are_keys else proj[:, qs + ks:qs + ks + self.v_size]) if self.own_kv else None
+        gated = self.gate is not None
+        heads = rt.workspace("attn_out", self.o_size, rt.dtype) if (gated or scale != 1.0 or not out.is_contiguous()) else out
         pos = self.position
         plan.window_attention(
-            q_in=proj[:, :qs], k_in=proj[:, qs:qs + ks] if self.own_kv else None, v_in=proj[:, qs + ks:] if self.own_kv else None,
+            q_in=proj[:, :qs], k_in=k_in, v_in=v_in,
             q_gain=self.q_gain, k_gain=self.k_gain, eps=self.eps or 0.0,
             inv_freq=pos.frequencies() if pos is not None else None, rot_dims=pos.dims if pos is not None else 0,
-            amplitude=pos.amplitude if pos is not None else 1.0, q=q, out=out, cache=cache.kv, group=cache.group,
+            amplitude=pos.amplitude if pos is not None else 1.0, q=q, out=heads, cache=cache.kv, group=cache.group,
             num_heads=self.nh, num_kv_heads=self.nkv, qk_dim=self.dk, v_dim=self.dv, window=self.window,
             keep_first=self.keep_first, scale=self.scale, sink=self.sink,
+            q_bias=self.q_bias, k_bias=self.k_bias, v_bias=self.v_bias, head_norm=self.head_norm,
             # up to 8 key ranges per decoded token: a maximum, a sum and an output row per range and head
             scratch=(rt.buffer("window_attention_scratch", 1, rt.max_requests * self.nh * 8 * (self.dv + 2), torch.float32,
                                exact=True).view(-1) if rt.dtype == torch.bfloat16 else None))
+        if gated:
+            g0 = self.in_size - self.o_size
+            plan.pointwise("sigmoid_mul", heads, proj[:, g0:g0 + self.o_size], out, scale=scale)
+        elif heads is not out:
+            raise ValueError(f"{self.prefix}: heads without a gate go to a dense place of their own, unscaled")
+
+    def emit(self, plan: Plan, h: torch.Tensor, cache) -> torch.Tensor:
+        rt = self.rt
+        proj = rt.workspace("qkv", self.w_in.shape[0], rt.dtype)
+        plan.linear(h, self.w_in, proj)
+        out = rt.workspace("attn_gated" if self.gate is not None else "attn_out", self.o_size, rt.dtype)
+        self.emit_heads(plan, proj, cache, out)
         delta = rt.workspace("mixer_out", self.hidden, torch.float32)
         plan.linear(out, self.w_o, delta)
         return delta

@@ -37,6 +37,8 @@ data in pages with a block table per request; False: a state of fixed size per r
 tensor for `count` pages or request slots), `bytes_per_token(dtype)` (paged: what one cached token costs,
 for sizing the pool), `zero_on_start` (state: cleared when a request starts) and
 `view(tensor, group, writes)` (what the mixer is handed).  The cache manager and the engine use only these.
+A paged spec may carry a `state` attribute, itself a non-paged spec: the run then also gets a state tensor (one
+row per request slot), and its `view` is called with `state_tensor=` as well (`PagedAndStateSpec`).
 """
 from __future__ import annotations
 
@@ -115,6 +117,84 @@ class StateSpec:
 
     def view(self, tensor: torch.Tensor, group: Optional[int], writes: bool) -> StateView:
         return StateView(tensor)
+
+
+@dataclass
+class StatesView:
+    """Several named states of one run: `states[name]` is [slots, *shape] (its rows may be strided: the states of a slot lie
+    side by side in one row of the run's tensor)."""
+
+    states: Dict[str, torch.Tensor]
+
+
+@dataclass(frozen=True)
+class StatesSpec:
+    """A mixer that keeps several 32-bit states of fixed size per request (`parts`: (name, shape) pairs), all zeroed when a
+    request starts.  They share one tensor [slots, total]; the view hands each out under its name."""
+
+    parts: Tuple[Tuple[str, Tuple[int, ...]], ...]
+    paged = False
+    window = 0
+    zero_on_start = True
+
+    @staticmethod
+    def _numel(shape: Tuple[int, ...]) -> int:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        return n
+
+    def allocate(self, count: int, page_size: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+        return torch.zeros(count, sum(self._numel(s) for _, s in self.parts), dtype=torch.float32, device=device)
+
+    def bytes_per_token(self, dtype: torch.dtype) -> int:
+        return 0
+
+    def view(self, tensor: torch.Tensor, group: Optional[int], writes: bool) -> StatesView:
+        out, at = {}, 0
+        for name, shape in self.parts:
+            n = self._numel(shape)
+            out[name] = tensor[:, at:at + n].unflatten(1, tuple(shape))
+            at += n
+        return StatesView(out)
+
+
+@dataclass
+class PagedAndStateView:
+    """What a mixer of several branches is handed: the pages of the branch that keeps keys and values, and the states of
+    the branches that keep a state of fixed size."""
+
+    paged: Any
+    state: Any
+
+
+@dataclass(frozen=True)
+class PagedAndStateSpec:
+    """A mixer that keeps BOTH pages (keys and values of earlier tokens, `paged_spec`) and a state of fixed size per request
+    (`state`, a non-paged spec).  Towards the cache manager it is the paged spec (pages, window, first positions kept); the
+    manager also makes the state tensor, one row per request slot, and clears a row when a request starts."""
+
+    paged_spec: Any
+    state: Any
+    paged = True
+
+    @property
+    def window(self) -> int:
+        return int(getattr(self.paged_spec, "window", 0))
+
+    @property
+    def keep_first(self) -> int:
+        return int(getattr(self.paged_spec, "keep_first", 0))
+
+    def allocate(self, count: int, page_size: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+        return self.paged_spec.allocate(count, page_size, dtype, device)
+
+    def bytes_per_token(self, dtype: torch.dtype) -> int:
+        return self.paged_spec.bytes_per_token(dtype)
+
+    def view(self, tensor: torch.Tensor, group: Optional[int], writes: bool, state_tensor: Optional[torch.Tensor] = None):
+        return PagedAndStateView(self.paged_spec.view(tensor, group, writes),
+                                 self.state.view(state_tensor, None, writes) if state_tensor is not None else None)
 
 
 class Part:

@@ -205,3 +205,69 @@ class PostNormResidualBlock(Part):
         x, _ = self.emit(plan, x, delta, cache)
         run_alone(self.rt, plan, batch)
         return x, None
+
+
+@register_part("block", "sandwich_residual")
+class SandwichResidualBlock(Part):
+    """x = x + norm1b(mixer(norm1(x)));  x = x + norm2b(feed_forward(norm2(x))): a norm before AND after each sublayer.
+    A layer may have no feed-forward (and then neither of its norms).
+
+    The stream is 32-bit.  The norm before a sublayer writes its input in the type of the products; the norm behind it
+    is the kernel that norms a sublayer's output and adds it to the stream in one pass.  The block reads the parts
+    "mixer", "mixer_norm", "mixer_out_norm" and, where the layer has a feed-forward, "feed_forward", "feed_forward_norm"
+    and "feed_forward_out_norm"."""
+
+    def __init__(self, rt: Runtime, prefix: str, layer: LayerSpec, mixer_name: str = "mixer", feed_forward_name: str = "feed_forward",
+                 mixer_norm_name: str = "mixer_norm", mixer_out_norm_name: str = "mixer_out_norm",
+                 feed_forward_norm_name: str = "feed_forward_norm", feed_forward_out_norm_name: str = "feed_forward_out_norm"):
+        super().__init__(rt, prefix)
+        has_ffn = "feed_forward" in layer.parts
+        need = ["mixer", "mixer_norm", "mixer_out_norm"] + (["feed_forward_norm", "feed_forward_out_norm"] if has_ffn else [])
+        missing = [n for n in need if n not in layer.parts]
+        if missing:
+            raise ValueError(f"layer {prefix!r}: a sandwich_residual block needs the parts {', '.join(missing)}")
+        self.mixer_norm = build_part("norm", layer.parts["mixer_norm"], rt, self.name(mixer_norm_name))
+        self.mixer = build_part("mixer", layer.parts["mixer"], rt, self.name(mixer_name))
+        self.mixer_out_norm = build_part("norm", layer.parts["mixer_out_norm"], rt, self.name(mixer_out_norm_name))
+        self.ffn = self.ffn_norm = self.ffn_out_norm = None
+        if has_ffn:
+            self.ffn_norm = build_part("norm", layer.parts["feed_forward_norm"], rt, self.name(feed_forward_norm_name))
+            self.ffn = build_part("feed_forward", layer.parts["feed_forward"], rt, self.name(feed_forward_name))
+            self.ffn_out_norm = build_part("norm", layer.parts["feed_forward_out_norm"], rt, self.name(feed_forward_out_norm_name))
+        self.parts = tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_out_norm, self.ffn_norm, self.ffn, self.ffn_out_norm)
+                           if p is not None)
+        for n in (self.mixer_out_norm, self.ffn_out_norm):
+            if n is not None and not (hasattr(n, "gain") and hasattr(n, "eps")):
+                raise ValueError(f"layer {prefix!r}: the norm on a sublayer's output needs a gain vector and an eps")
+        self.capture_safe = all(p.capture_safe and hasattr(p, "emit") for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+                                if p is not None)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        out: Dict[str, WeightSpec] = {}
+        for p in self.parts:
+            out.update(p.weight_specs())
+        return out
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for p in self.parts:
+            p.load_weights({n: tensors[n] for n in p.weight_specs()})
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def emit(self, plan: Plan, x: torch.Tensor, delta: Optional[torch.Tensor], cache):
+        hidden = x.shape[1]
+        h = emit_norm(plan, self.mixer_norm, x, delta=delta)
+        a = emit_mixer(plan, self.mixer, h, cache, hidden)
+        plan.postnorm(x, a, self.mixer_out_norm.gain, self.mixer_out_norm.eps)
+        if self.ffn is not None:
+            h = emit_norm(plan, self.ffn_norm, x)
+            b = emit_feed_forward(plan, self.ffn, h, hidden)
+            plan.postnorm(x, b, self.ffn_out_norm.gain, self.ffn_out_norm.eps)
+        return x, None
+
+    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], batch, cache):
+        plan = Plan()
+        x, _ = self.emit(plan, x, delta, cache)
+        run_alone(self.rt, plan, batch)
+        return x, None

@@ -11,7 +11,8 @@ from .base import Part, Runtime, WeightSpec, register_part, run_alone
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Part):
-    """x[t,:] = E[ids[t],:] as 32-bit, no scaling (src/runtime/kernels/cpu_kernels.cpp:262-274).
+    """x[t,:] = E[ids[t],:] as 32-bit (src/runtime/kernels/cpu_kernels.cpp:262-274), times the constant `scale` where a
+    design has one (the product is formed in 32-bit).
 
     `leaf` is the table's name below the prefix ("" = the prefix itself).  `extra_tables` (full tensor name ->
     width) are further per-token tables [vocab, width] that the part only stores: other parts of the model take
@@ -19,10 +20,11 @@ class TokenEmbedding(Part):
 
     def __init__(self, rt: Runtime, prefix: str, vocab_size: int, hidden_size: int, leaf: str = "weight",
                  extra_tables: Optional[Dict[str, int]] = None, norm_leaf: Optional[str] = None,
-                 norm_eps: Optional[float] = None):
+                 norm_eps: Optional[float] = None, scale: float = 1.0):
         super().__init__(rt, prefix)
         self.vocab, self.hidden = int(vocab_size), int(hidden_size)
         self.leaf = leaf
+        self.scale = float(scale)
         # with `norm_leaf`, the gathered rows are RMS-normed with that gain vector before they enter the stream
         self.norm_leaf, self.norm_eps = norm_leaf, None if norm_eps is None else float(norm_eps)
         if (norm_leaf is None) != (norm_eps is None):
@@ -53,7 +55,7 @@ class TokenEmbedding(Part):
 
     def emit(self, plan: Plan) -> torch.Tensor:
         x = self.rt.workspace("residual", self.hidden, torch.float32)
-        plan.embedding(self.table, x)
+        plan.embedding(self.table, x, scale=self.scale)
         if self.norm_leaf is not None:
             # the stream in the type of the products too: a block whose sublayers read the stream itself finds it there
             copy = None if self.rt.dtype == torch.float32 else self.rt.workspace("stream_copy", self.hidden, self.rt.dtype)

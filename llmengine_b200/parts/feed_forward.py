@@ -102,15 +102,18 @@ GATED_ACTIVATIONS = ("silu", "clamped_swish")
 
 @register_part("feed_forward", "gated_dense")
 class GatedDense(Part):
-    """down( act(gate(h), up(h)) ), no biases, tensors gate / up / down, the activation a parameter:
+    """down( act(gate(h), up(h)) ), tensors gate / up / down (with `biases`: every projection has one, <tensor>.b, added
+    in 32-bit to the product before the activation and behind the last product), the activation a parameter:
     "silu": g sigmoid(g) u;  "clamped_swish" with `limit` (and `slope`, 1.702 unless given): g' = min(g, limit),
     u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1).  The gate and up matrices are stored as one matrix so
     that one product serves both, with the activation in its epilogue where a kernel has it."""
 
     def __init__(self, rt: Runtime, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "silu",
-                 limit: Optional[float] = None, slope: float = 1.702):
+                 limit: Optional[float] = None, slope: float = 1.702, biases: bool = False):
         super().__init__(rt, prefix)
         self.hidden, self.inter = int(hidden_size), int(intermediate_size)
+        self.biases = bool(biases)
+        self.b_gate_up = self.b_down = None
         if activation not in GATED_ACTIVATIONS:
             raise ValueError(f"{prefix}: unknown gated activation {activation!r}; known: {', '.join(GATED_ACTIVATIONS)}")
         if activation == "clamped_swish" and limit is None:
@@ -120,20 +123,28 @@ class GatedDense(Part):
         self.w_gate_up = self.w_down = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {self.name("gate"): WeightSpec((self.inter, self.hidden)), self.name("up"): WeightSpec((self.inter, self.hidden)),
-                self.name("down"): WeightSpec((self.hidden, self.inter))}
+        s = {self.name("gate"): WeightSpec((self.inter, self.hidden)), self.name("up"): WeightSpec((self.inter, self.hidden)),
+             self.name("down"): WeightSpec((self.hidden, self.inter))}
+        if self.biases:
+            s[self.name("gate.b")] = WeightSpec((self.inter,), role="vector")
+            s[self.name("up.b")] = WeightSpec((self.inter,), role="vector")
+            s[self.name("down.b")] = WeightSpec((self.hidden,), role="vector")
+        return s
 
     def load_weights(self, t: Dict[str, torch.Tensor]) -> None:
         self.w_gate_up = torch.cat([t[self.name("gate")], t[self.name("up")]], 0).contiguous()
         self.w_down = t[self.name("down")].contiguous()
+        if self.biases:
+            self.b_gate_up = torch.cat([t[self.name("gate.b")].float(), t[self.name("up.b")].float()]).contiguous()
+            self.b_down = t[self.name("down.b")].float().contiguous()
 
     def emit(self, plan: Plan, h: torch.Tensor, out_name: str = "ffn_out") -> torch.Tensor:
         rt = self.rt
         act = rt.workspace("act", self.inter, rt.dtype)
         gate_up = rt.workspace("gate_up", 2 * self.inter, rt.dtype)
-        plan.linear_swiglu(h, self.w_gate_up, gate_up, act, act=self.act, params=self.params)
+        plan.linear_swiglu(h, self.w_gate_up, gate_up, act, act=self.act, params=self.params, bias=self.b_gate_up)
         delta = rt.workspace(out_name, self.hidden, torch.float32)
-        plan.linear(act, self.w_down, delta)
+        plan.linear(act, self.w_down, delta, bias=self.b_down)
         return delta
 
     def forward(self, h: torch.Tensor, batch=None) -> torch.Tensor:

@@ -54,3 +54,16 @@ class ScalarGainRMSNorm(RMSNorm):
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.gain = tensors[self.name(self.leaf)].reshape(1).expand(self.size).contiguous()
+
+
+@register_part("norm", "rmsnorm_one_plus")
+class OnePlusRMSNorm(RMSNorm):
+    """y = x / sqrt(mean(x^2) + eps) * (1 + w): the stored vector w lies around zero.  1 + w is formed once in 32-bit when
+    the weights are loaded; the kernels are those of the norm with a gain vector (as a pre-norm, and as the norm on a
+    sublayer's output, which reads `gain` and `eps`)."""
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {self.name(self.leaf): WeightSpec((self.size,), role="vector", init="normal")}
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.gain = (1.0 + tensors[self.name(self.leaf)].float()).contiguous()

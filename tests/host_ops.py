@@ -23,8 +23,8 @@ class HostOps:
     def compile(self, plan):
         return HostPlan(self, plan)
 
-    def embedding(self, ids, table, out):
-        out.copy_(table[ids.long()].float())
+    def embedding(self, ids, table, out, scale=1.0):
+        out.copy_(table[ids.long()].float() * scale)
         return out
 
     def rmsnorm(self, x, gain, eps, out, delta=None, rows=None):
@@ -97,14 +97,17 @@ class HostOps:
     # the fast kernels share the plain one's semantics
     attention = attention_plain
 
-    def swiglu(self, gate_up, out):
+    def swiglu(self, gate_up, out, bias=None):
         inter = out.shape[1]
         g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+        if bias is not None:
+            g, u = (g + bias[:inter]).to(out.dtype).float(), (u + bias[inter:]).to(out.dtype).float()
         out.copy_(((g / (1.0 + torch.exp(-g))) * u).to(out.dtype))
         return out
 
-    def linear(self, x, w, out):
-        out.copy_((x.float() @ w.float().t()).to(out.dtype))
+    def linear(self, x, w, out, bias=None):
+        y = x.float() @ w.float().t()
+        out.copy_((y if bias is None else y.to(out.dtype).float() + bias).to(out.dtype))
         return out
 
     def activation(self, act, params, x, out):
@@ -113,9 +116,76 @@ class HostOps:
         ap, an = params
         out.copy_(torch.where(z > 0, ap * z * z + 0.5 * z, an * (torch.expm1(torch.clamp(z, max=0)) - z) + 0.5 * z).to(out.dtype))
 
-    def pointwise(self, kind, a, b, out):
+    def pointwise(self, kind, a, b, out, scale=1.0):
         assert kind == "sigmoid_mul"
-        out.copy_((a.float() * torch.sigmoid(b.float())).to(out.dtype))
+        out.copy_((a.float() * torch.sigmoid(b.float()) * scale).to(out.dtype))
+
+    # ---- layers with a state of fixed size per request
+    @staticmethod
+    def _requests(batch):
+        cu = batch.cu_q_lens.tolist()
+        return [(cu[r], cu[r + 1], int(batch.state_slots[r])) for r in range(len(cu) - 1)]
+
+    def short_conv(self, a, batch):
+        w, K = a["w"], a["w"].shape[1]
+        for lo, hi, slot in self._requests(batch):
+            if hi == lo:
+                continue
+            x = a["x"][lo:hi].float()
+            past = a["state"][slot][: K - 1] if K > 1 else x[:0]
+            full = torch.cat([past, x], 0)
+            y = a["bias"].float().expand(hi - lo, -1).clone() if a["bias"] is not None else torch.zeros_like(x)
+            for j in range(K):
+                y += full[K - 1 - j: K - 1 - j + (hi - lo)] * w[:, K - 1 - j]
+            a["out"][lo:hi] = y * torch.sigmoid(y) if a["act"] == "silu" else y
+            if K > 1:
+                a["state"][slot][: K - 1] = full[-(K - 1):]
+
+    def rotate(self, a, T, positions):
+        for x, out, heads, scale in zip(a["x"], a["out"], a["heads"], a["scale"]):
+            if x is None:
+                continue
+            v = x[:T].float().view(T, heads, a["dim"])
+            if a["rot_dims"]:
+                half = a["rot_dims"] // 2
+                ang = positions.float()[:, None] * a["inv_freq"][None, :]
+                c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+                u, w = v[..., :half], v[..., half:2 * half]
+                v = torch.cat([u * c - w * s, w * c + u * s, v[..., 2 * half:]], -1)
+            out[:T] = v.reshape(T, -1) * scale
+
+    def recurrence(self, a, batch):
+        H, n, p, G = a["heads"], a["n"], a["p"], a["qk_groups"]
+        rep = H // G
+        for lo, hi, slot in self._requests(batch):
+            S = a["state"][slot]                                           # [H, p, n]
+            for t in range(lo, hi):
+                q = a["q"][t].view(G, n).repeat_interleave(rep, 0)
+                k = a["k"][t].view(G, n).repeat_interleave(rep, 0)
+                v = a["v"][t].float().view(H, p)
+                if a["dt"] is None:
+                    decay, step = a["decay"], torch.ones(H)
+                else:
+                    z = a["dt"][t].float() + (a["dt_bias"] if a["dt_bias"] is not None else 0.0)
+                    step = torch.clamp(z, min=0) + torch.log1p(torch.exp(-z.abs()))
+                    decay = torch.exp(-torch.exp(a["a_log"]) * step)
+                S.mul_(decay[:, None, None]).add_((step[:, None] * v)[:, :, None] * k[:, None, :])
+                y = torch.einsum("hpn,hn->hp", S, q)
+                if a["skip"] is not None:
+                    y = y + a["skip"][:, None] * v
+                a["out"][t] = y.reshape(-1)
+
+    def gated_norm(self, a, T):
+        y, g = a["y"][:T], a["gate"][:T].float()
+        gate = g * torch.sigmoid(g)
+        u = y * gate if a["gate_first"] else y
+        parts = u.view(T, -1, a["group"])
+        u = (parts / torch.sqrt((parts * parts).mean(-1, keepdim=True) + a["eps"])).reshape(T, -1)
+        if a["weight"] is not None:
+            u = u * a["weight"]
+        if not a["gate_first"]:
+            u = u * gate
+        a["out"][:T] = (u * a["scale"]).to(a["out"].dtype)
 
     def batched_linear(self, x, w, out):
         out.copy_(torch.einsum("tbk,bnk->tbn", x.float(), w.float()).to(out.dtype))
@@ -182,9 +252,15 @@ class HostOps:
         keys = pages[:, :G * ps * dk].view(-1, G, ps, dk)
         vals = pages[:, G * ps * dk:].view(-1, G, ps, dv)
 
-        def finish(x, heads, gain):
-            x = x[:T].float()
-            if gain is not None:
+        def biased(x, bias):
+            return x[:T] if bias is None else (x[:T].float() + bias).to(x.dtype)
+
+        def finish(x, heads, gain, bias=None):
+            x = biased(x, bias).float()
+            if gain is not None and a.get("head_norm"):
+                x = x.view(T, heads, dk)
+                x = (x * (1.0 / torch.sqrt((x * x).mean(-1, keepdim=True) + a["eps"])) * gain).reshape(T, -1)
+            elif gain is not None:
                 x = x * (1.0 / torch.sqrt((x * x).mean(-1, keepdim=True) + a["eps"])) * gain
             x = x.view(T, heads, dk)
             if a["inv_freq"] is not None:
@@ -194,11 +270,11 @@ class HostOps:
                 u, v = x[..., :half], x[..., half:2 * half]
                 x = torch.cat([u * c - v * s, v * c + u * s, x[..., 2 * half:]], -1)
             return x
-        q = finish(a["q_in"], H, a["q_gain"]).to(cache.dtype)
+        q = finish(a["q_in"], H, a["q_gain"], a.get("q_bias")).to(cache.dtype)
         a["q"][:T] = q.reshape(T, -1)
         if a["k_in"] is not None:
-            k = finish(a["k_in"], G, a["k_gain"]).to(cache.dtype)
-            v = a["v_in"][:T].reshape(T, G, dv)
+            k = finish(a["k_in"], G, a["k_gain"], a.get("k_bias")).to(cache.dtype)
+            v = biased(a["v_in"], a.get("v_bias")).reshape(T, G, dv)
             for t in range(T):
                 slot = int(slot_mapping[t])
                 if slot >= 0:
@@ -292,7 +368,7 @@ class HostPlan:
         for op in self.plan.ops[first:last]:
             a, k = op.a, op.kind
             if k == "embedding":
-                o.embedding(batch.token_ids, a["table"], a["out"][:T])
+                o.embedding(batch.token_ids, a["table"], a["out"][:T], a.get("scale", 1.0))
             elif k == "rmsnorm":
                 some = a["rows"] == "logits"
                 o.rmsnorm(a["x"][:T], a["gain"], a["eps"], a["out"][:n_rows(a["rows"])], delta=cut(a["delta"]),
@@ -300,12 +376,21 @@ class HostPlan:
             elif k == "linear":
                 n = n_rows(a["rows"])
                 if n:
-                    o.linear(a["x"][:n], a["w"], batch.logits if a["out"] is None else a["out"][:n])
+                    o.linear(a["x"][:n], a["w"], batch.logits if a["out"] is None else a["out"][:n], a.get("bias"))
+            elif k == "short_conv":
+                o.short_conv(a, batch)
+            elif k == "rotate":
+                o.rotate(a, T, batch.positions)
+            elif k == "recurrence":
+                o.recurrence(a, batch)
+            elif k == "gated_norm":
+                o.gated_norm(a, T)
             elif k == "linear_swiglu":
                 o.linear(a["x"][:T], a["w_gate_up"], a["gate_up"][:T])
                 if a.get("act", "silu") == "silu":
-                    o.swiglu(a["gate_up"][:T], a["out"][:T])
+                    o.swiglu(a["gate_up"][:T], a["out"][:T], a.get("bias"))
                 else:
+                    assert a.get("bias") is None
                     o.gated_act(a["act"], a["params"], a["gate_up"][:T], a["out"][:T])
             elif k == "postnorm":
                 o.postnorm(a["x"][:T], cut(a["y"]), a["gain"], a["eps"], a["accumulate"], cut(a["copy"]))
@@ -337,7 +422,7 @@ class HostPlan:
                 o.linear(a["x"][:T], a["w"], a["mid"][:T])
                 o.activation(a["act"], a["params"], a["mid"][:T], a["out"][:T])
             elif k == "pointwise":
-                o.pointwise(a["what"], a["a"][:T], cut(a["b"]), a["out"][:T])
+                o.pointwise(a["what"], a["a"][:T], cut(a["b"]), a["out"][:T], a.get("scale", 1.0))
             elif k == "batched_linear":
                 o.batched_linear(a["x"][:T], a["w"], a["out"][:T])
             elif k == "residual_add":
