@@ -193,7 +193,7 @@ class CacheManager:
         """Bring the device block tables and the states of newly started requests up to date, without
         waiting for the device: the changed table entries travel as (position, value) pairs through a
         small ring of pinned buffers and are scattered into the tables by the stream."""
-        if not self.tables_dev:
+        if not self.tables_dev and not self.state:       # nothing lives on a device (yet)
             self._dirty = [dict() for _ in self.groups]
             self._new_slots = []
             return
