@@ -1,4 +1,4 @@
-"""A design beside its closest existing model at equal size (`python bench.py --design bepuzen | torisun`).
+"""A design beside its closest existing model at equal size (`python bench.py --design bepuzen | torisun | vifelix`).
 
 For each size: prefill of one 2,048-token prompt and decode at batch 1 / 8 / 64 over 2,048 cached tokens, tokens/s,
 for the design and for the grouped-query model of the same width, depth and (active) weight count per layer;
@@ -13,6 +13,9 @@ import statistics
 from typing import Any, Dict, List
 
 L1, L2 = "latent_attention", "latent_attention_2"
+# a 32-bit operation outside the tensor cores counts as this many operations of the bf16 product peak that the tables divide
+# by (set by `run` from the measured peak), so that `ideal` is its time at the 32-bit ceiling
+FP32_SHARE = 1.0
 
 
 def bepuzen_shape(layers: int, width: int, heads: int, ff: int, kv_rank: int = 512, dim: int = 128, rot: int = 64,
@@ -57,6 +60,26 @@ def torisun_shape(layers: int, width: int, heads: int, kv_heads: int, ff: int, e
     return {"architecture": "Torisun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": out}
 
 
+def vifelix_shape(width: int, heads: int, kv_heads: int, ff: int, ssm_heads: int, retention_heads: int, window: int = 1024,
+                  dim: int = 128, state: int = 128, vocab: int = 32768) -> Dict[str, Any]:
+    """Six layers: state-space layers without feed-forward around two parallel layers (window attention beside retention)
+    with one.  The state-space mixer is twice the width inside, in heads of 64."""
+    mamba = {"type": "mamba2", "mlp": None,
+             "mixer": {"heads": ssm_heads, "vdim": 64, "state": state, "groups": 8, "conv": 4, "norm_groups": 8}}
+    par = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff}, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
+                 "rot": {"base": 500000.0, "dims": dim // 2}},
+        "right": {"heads": retention_heads, "dim": dim, "vdim": dim, "decay": [1.0 - 2.0 ** (-5 - i % 6) for i in range(retention_heads)],
+                  "rot": {"base": 1000000.0, "dims": dim}},
+        "left_scale": 1.2, "right_scale": 1.1}}
+    return {"architecture": "Vifelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": width ** 0.5},
+            "layers": [mamba, par, mamba, mamba, par, mamba]}
+
+
+# 32-bit multiply-adds outside the tensor cores: 148 SMs x 128 lanes x 2 x 1.965 GHz (nominal), the compute ceiling of a
+# recurrence whose state and inputs are 32-bit
+FP32_TFLOPS = 74.4
+
 # name -> (layers timed, the design's shape, the grouped-query model of the same width and feed-forward weight count)
 TORISUN_SIZES = {
     "2048": (6, torisun_shape(6, 2048, 16, 4, 5504, 32, 4, 1024), gqa_shape(6, 2048, 16, 5504)),
@@ -65,6 +88,10 @@ TORISUN_SIZES = {
 SIZES = {
     "2048": (6, bepuzen_shape(6, 2048, 16, 8192), gqa_shape(6, 2048, 16, 5504)),
     "4096": (6, bepuzen_shape(6, 4096, 32, 16384), gqa_shape(6, 4096, 32, 10944)),
+}
+VIFELIX_SIZES = {
+    "2048": (6, vifelix_shape(2048, 16, 4, 5504, 64, 8), gqa_shape(6, 2048, 16, 5504)),
+    "4096": (6, vifelix_shape(4096, 32, 8, 10944, 128, 16), gqa_shape(6, 4096, 32, 10944)),
 }
 CACHED, PROMPT = 2048, 2048
 
@@ -139,6 +166,21 @@ def record_cost(op, T: int, keys_per_row: float, cache_rows: float):
         return f"pointwise {a['what']}", 0.0, 3 * T * a["out"].shape[1] * el
     if k == "residual_add":
         return "residual add", 0.0, T * a["x"].shape[1] * 16
+    requests = T if T <= cache_rows / 2 else 1                            # a decode step has one token a request
+    if k == "short_conv":
+        C, K = a["w"].shape
+        return (f"short convolution {C}x{K}", 2.0 * T * C * K * FP32_SHARE,
+                T * C * (a["x"].element_size() + 4) + C * (K + 1) * 4 + requests * 2 * (K - 1) * C * 4)
+    if k == "rotate":
+        cols = sum(h for x_, h in zip(a["x"], a["heads"]) if x_ is not None) * a["dim"]
+        return f"rotation into 32-bit, {cols} columns", 0.0, T * cols * (el + 4)
+    if k == "recurrence":
+        H, n, p, G = a["heads"], a["n"], a["p"], a["qk_groups"]
+        return (f"recurrence {H} heads, state {n}x{p}" + (", decay per token" if a.get("dt") is not None else ", fixed decay"),
+                4.0 * T * H * n * p * FP32_SHARE, requests * 2 * H * n * p * 4 + T * (2 * G * n * 4 + H * p * (a["v"].element_size() + 4)))
+    if k == "gated_norm":
+        cols = a["y"].shape[1]
+        return f"gate + norm in groups of {a['group']}", 0.0, T * cols * (4 + 2 * el)
     return k, 0.0, 0.0
 
 
@@ -283,7 +325,9 @@ def run(args, pk) -> int:
 
     import torch
     design_name = getattr(args, "design", None) or "bepuzen"
-    table_of_sizes = {"bepuzen": SIZES, "torisun": TORISUN_SIZES}[design_name]
+    table_of_sizes = {"bepuzen": SIZES, "torisun": TORISUN_SIZES, "vifelix": VIFELIX_SIZES}[design_name]
+    global FP32_SHARE
+    FP32_SHARE = pk["bf16_tflops"] / FP32_TFLOPS
     sizes = [args.size] if getattr(args, "size", None) else list(table_of_sizes)
     rec: Dict[str, Any] = {"metric": f"{design_name.capitalize()} beside the grouped-query model of equal size, bf16: tokens/s and per-record rooflines",
                            "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic token ids, random weights",
