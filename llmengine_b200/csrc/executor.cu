@@ -729,7 +729,7 @@ int op_recurrence(LlmeExecutor& ex, const LlmeRecurrenceOp& o, const LlmeStep& s
     if (!f) return ex.fail("no recurrence kernel is registered");
     LlmeRecurrenceArgs a = {o.q, o.k, o.ldq, o.ldk, o.qk_groups, o.v, o.ldv, o.v_dtype, o.gate, o.decay, o.dt, o.lddt, o.dt_dtype, o.dt_bias,
                             o.a_log, o.skip, o.state, o.state_stride, o.out, o.ldo, s.cu_q_lens, s.state_slots, s.num_requests, o.heads,
-                            o.n, o.p};
+                            o.n, o.p, o.scratch, o.scratch_floats, s.num_tokens, s.max_portion_len > 1 ? s.max_portion_len : 1};
     return ex.launched(f(&a, st), "recurrence");
 }
 

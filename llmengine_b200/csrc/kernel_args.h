@@ -162,6 +162,8 @@ typedef struct LlmeRecurrenceArgs {
     float* out; long long ldo;                               /* [T, heads * p] 32-bit */
     const int* cu_q_lens; const int* state_slots;
     int requests, heads, n, p;
+    float* scratch; long long scratch_floats;                /* room for the states of pieces of long requests, or NULL */
+    int tokens, max_len;                                     /* of the step; the most tokens one request brings */
 } LlmeRecurrenceArgs;
 
 /* RMS norm in groups of `group` columns with a gate (silu of a second tensor) before or after it:

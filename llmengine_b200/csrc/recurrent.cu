@@ -135,12 +135,12 @@ LLME_API int llme_rotate(const LlmeRotateArgs* args, cudaStream_t stream) {
 }
 
 // ----------------------------------------------------------------------------- the recurrence
-// One warp owns one column of a head's state (the n values that meet one coordinate of v): lane l holds S[l + 32 r], r < R,
-// in registers for all tokens of the request's portion; a token costs R multiply-adds for the update, R for the output and
-// one sum over the lanes.  Columns are independent, so no warp waits for another.  A block takes WARPS columns of one
-// (request, head); the state is stored column by column, so a warp's loads and stores of it are contiguous.
+// Single tokens (and states with fewer than four columns): one warp owns one column of a head's state (the n values that meet
+// one coordinate of v): lane l holds S[l + 32 i], i < R, in registers; a token costs R multiply-adds for the update, R for the
+// output and one sum over the lanes.  Columns are independent, so no warp waits for another.  A block takes WARPS columns of
+// one (request, head); the state is stored column by column, so a warp's loads and stores of it are contiguous.
 template <int R>
-__global__ void __launch_bounds__(256) recurrence_kernel(LlmeRecurrenceArgs a) {
+__global__ void __launch_bounds__(256) recurrence_column_kernel(LlmeRecurrenceArgs a) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
@@ -167,13 +167,12 @@ __global__ void __launch_bounds__(256) recurrence_kernel(LlmeRecurrenceArgs a) {
             step = softplus32(load_as_f32(a.dt, a.dt_dtype, (size_t)t * a.lddt + h) + bias);
             decay = expf(rate * step);
         }
-        const float sv = step;
         float y = 0.0f;
 #pragma unroll
         for (int i = 0; i < R; ++i) {
             const int e = lane + 32 * i;
             if (e < n) {
-                S[i] = fmaf(decay, S[i], (sv * k[e]) * v);
+                S[i] = fmaf(decay, S[i], (step * k[e]) * v);
                 y = fmaf(S[i], q[e], y);
             }
         }
@@ -185,6 +184,266 @@ __global__ void __launch_bounds__(256) recurrence_kernel(LlmeRecurrenceArgs a) {
         if (lane + 32 * i < n) st[lane + 32 * i] = S[i];
 }
 
+// Portions of prompts: a block of eight warps takes 32 neighbouring columns of one (request or piece of it, head), four a warp
+// (lane l holds S[l + 32 i] of each of its four).  The block brings q and k of a few tokens at a time into shared memory with
+// asynchronous copies, and v, the steps and the decays beside them, while it works on the tokens before: every warp of the
+// block needs the same q and k, and no token's operands come from global memory when they are due.  A token costs a warp 4 R
+// multiply-adds for the update, 4 R for the output, and six exchanges that sum the four columns over the lanes (each lane
+// ending with the sum of one column).
+//
+// A request with many tokens in the step is cut into pieces of `chunk` tokens that run side by side, in three launches:
+// every piece but a request's last starts from zero and leaves E_c, what its tokens alone add to the state, and D_c, the
+// product of its decays; then, per state element and in the pieces' order, B_0 = the stored state, B_(c+1) = D_c B_c + E_c
+// gives every piece the state it starts from; then every piece runs from B_c, writes its outputs, and the last one stores
+// the state.  The sum is the one of the plain walk in another order, all of it 32-bit.
+enum { REC_WHOLE = 0, REC_LOCAL = 1, REC_FROM_START = 2 };
+constexpr int REC_MIN_CHUNK = 64, REC_COLUMNS = 32;
+
+struct RecPiece { int r, index, pieces, slot; };
+
+// Piece z of the step when every request is cut each `chunk` tokens; `slot` counts the pieces of requests with several.
+__device__ __forceinline__ bool rec_find_piece(const int* __restrict__ cu, int requests, int chunk, int z, RecPiece& o) {
+    int multi = 0;
+    for (int i = 0; i < requests; ++i) {
+        const int np = (cu[i + 1] - cu[i] + chunk - 1) / chunk;
+        if (z < np) { o.r = i; o.index = z; o.pieces = np; o.slot = multi + z; return true; }
+        z -= np;
+        if (np > 1) multi += np;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void copy_async_4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+template <int R> struct RecTile {
+    static constexpr int TOKENS = R <= 4 ? 16 : (R == 8 ? 8 : 4);       // tokens in shared memory at a time, twice
+    static constexpr int ROW = 32 * R;                                   // n rounded up
+    static constexpr int V_EACH = (TOKENS * REC_COLUMNS + 255) / 256;    // values of v a thread fetches
+    float q[2][TOKENS][ROW], k[2][TOKENS][ROW], v[2][TOKENS][REC_COLUMNS], step[2][TOKENS], decay[2][TOKENS];
+    float sums[8][TOKENS][16];                                         // per warp and token: four partial sums of each of four columns
+};
+
+template <int R, bool LOCAL>
+__global__ void __launch_bounds__(256, R <= 4 ? 3 : 1) recurrence_tile_kernel(LlmeRecurrenceArgs a, int pass, int chunk, int slots, int vec) {
+    using Tile = RecTile<R>;
+    constexpr int TT = Tile::TOKENS, ROW = Tile::ROW, V_EACH = Tile::V_EACH;
+    __shared__ __align__(16) Tile sm;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int jb = blockIdx.x * REC_COLUMNS, j0 = jb + 4 * warp;        // the block's and the warp's first column
+    const int h = blockIdx.y, n = a.n, p = a.p;
+    RecPiece pc = {(int)blockIdx.z, 0, 1, 0};
+    if (pass != REC_WHOLE && !rec_find_piece(a.cu_q_lens, a.requests, chunk, blockIdx.z, pc)) return;
+    const bool last_piece = pc.index == pc.pieces - 1;
+    if (LOCAL && last_piece) return;
+    int first = a.cu_q_lens[pc.r], last = a.cu_q_lens[pc.r + 1];
+    if (pass != REC_WHOLE) {
+        first += pc.index * chunk;
+        last = min(last, first + chunk);
+    }
+    const bool active = j0 < p;
+    const size_t hpn = (size_t)a.heads * p * n, column = ((size_t)h * p + j0) * n;
+    float* kept = a.state + (size_t)a.state_slots[pc.r] * a.state_stride + column;
+    float* mine = pc.pieces > 1 ? a.scratch + (size_t)pc.slot * hpn + column : nullptr;
+    const float* from = LOCAL || !active ? nullptr : (mine ? mine : kept);
+    float S[4][R];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < R; ++i)
+            S[c][i] = from && j0 + c < p && lane + 32 * i < n ? from[(size_t)c * n + lane + 32 * i] : 0.0f;
+    const int g = h / (a.heads / a.qk_groups);
+    const float fixed = a.gate == 0 ? a.decay[h] : 0.0f;
+    const float rate = a.gate == 1 ? -expf(a.a_log[h]) : 0.0f;
+    const float bias = a.gate == 1 && a.dt_bias ? a.dt_bias[h] : 0.0f;
+    const float skip = a.skip ? a.skip[h] : 0.0f;
+    const float* qg = a.q + (size_t)g * n;
+    const float* kg = a.k + (size_t)g * n;
+
+    float v_next[V_EACH], dt_next = 0.0f;
+    // Sends for the tokens t0 .. t0 + TT - 1: q and k straight into buffer b, v and dt into registers for now.
+    auto fetch = [&](int t0, int b) {
+        if (vec) {
+            for (int idx = tid; idx < TT * (ROW / 4); idx += 256) {
+                const int u = idx / (ROW / 4), e = (idx % (ROW / 4)) * 4, t = t0 + u;
+                if (e >= n) continue;
+                if (t < last) {
+                    copy_async_16(&sm.q[b][u][e], qg + (size_t)t * a.ldq + e);
+                    copy_async_16(&sm.k[b][u][e], kg + (size_t)t * a.ldk + e);
+                } else {
+                    *(float4*)&sm.q[b][u][e] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    *(float4*)&sm.k[b][u][e] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+            }
+        } else {
+            for (int idx = tid; idx < TT * ROW; idx += 256) {
+                const int u = idx / ROW, e = idx % ROW, t = t0 + u;
+                if (e >= n) continue;
+                if (t < last) {
+                    copy_async_4(&sm.q[b][u][e], qg + (size_t)t * a.ldq + e);
+                    copy_async_4(&sm.k[b][u][e], kg + (size_t)t * a.ldk + e);
+                } else sm.q[b][u][e] = sm.k[b][u][e] = 0.0f;
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < V_EACH; ++m) {
+            const int idx = tid + 256 * m, u = idx / REC_COLUMNS, c = idx % REC_COLUMNS, t = t0 + u;
+            v_next[m] = u < TT && t < last && jb + c < p ? load_as_f32(a.v, a.v_dtype, (size_t)t * a.ldv + (size_t)h * p + jb + c) : 0.0f;
+        }
+        dt_next = tid < TT && a.gate == 1 && t0 + tid < last ? load_as_f32(a.dt, a.dt_dtype, (size_t)(t0 + tid) * a.lddt + h) : 0.0f;
+    };
+    // Completes buffer b; a token past the end gets what changes nothing: q = k = v = 0, step 0, decay 1.
+    auto land = [&](int t0, int b) {
+#pragma unroll
+        for (int m = 0; m < V_EACH; ++m) {
+            const int idx = tid + 256 * m, u = idx / REC_COLUMNS, c = idx % REC_COLUMNS;
+            if (u < TT) sm.v[b][u][c] = v_next[m];
+        }
+        if (tid < TT) {
+            float st = 0.0f, dc = 1.0f;
+            if (t0 + tid < last) {
+                st = a.gate == 1 ? softplus32(dt_next + bias) : 1.0f;
+                dc = a.gate == 1 ? expf(rate * st) : fixed;
+            }
+            sm.step[b][tid] = st;
+            sm.decay[b][tid] = dc;
+        }
+        copy_async_wait();
+        __syncthreads();
+    };
+
+    const int tiles = (last - first + TT - 1) / TT;
+    if (n < ROW)                                                       // the rows' padding stays zero
+        for (int idx = tid; idx < 2 * TT * ROW; idx += 256)
+            if (idx % ROW >= n) (&sm.q[0][0][0])[idx] = (&sm.k[0][0][0])[idx] = 0.0f;
+    if (tiles > 0) {
+        const int t0 = first + (LOCAL ? tiles - 1 : 0) * TT;
+        fetch(t0, 0);
+        land(t0, 0);
+    }
+    // A piece's own addition to the state is taken from its last token backwards: E = sum_u (s_u prod_(u' > u) a_u') k_u v_u^T,
+    // one multiply-add an element and token, with `total` the product of the decays of the tokens behind.
+    float total = 1.0f;
+    for (int i = 0; i < tiles; ++i) {
+        const int b = i & 1, tile = LOCAL ? tiles - 1 - i : i, t0 = first + tile * TT;
+        const int next = first + (LOCAL ? tile - 1 : tile + 1) * TT;
+        if (i + 1 < tiles) fetch(next, b ^ 1);
+        if (active && LOCAL) {
+#pragma unroll 4
+            for (int u = TT - 1; u >= 0; --u) {
+                const float w = sm.step[b][u] * total;
+                const float4 v4 = *(const float4*)&sm.v[b][u][4 * warp];
+                const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const float kw = w * sm.k[b][u][lane + 32 * r];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) S[c][r] = fmaf(kw, v[c], S[c][r]);
+                }
+                total *= sm.decay[b][u];
+            }
+        } else if (active) {
+#pragma unroll 4
+            for (int u = 0; u < TT; ++u) {
+                const float step = sm.step[b][u], decay = sm.decay[b][u];
+                const float4 v4 = *(const float4*)&sm.v[b][u][4 * warp];
+                const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+                float y[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const float qi = sm.q[b][u][lane + 32 * r], ks = step * sm.k[b][u][lane + 32 * r];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        S[c][r] = fmaf(decay, S[c][r], ks * v[c]);
+                        y[c] = fmaf(S[c][r], qi, y[c]);
+                    }
+                }
+                // lanes 16..31 take over columns 2 and 3, then of each half the lanes with bit 3 set the odd column; after one
+                // more exchange lanes 8 c .. 8 c + 3 hold four parts of column c, which go to shared memory
+                const bool upper = lane & 16, odd = lane & 8;
+                const float k0 = (upper ? y[2] : y[0]) + __shfl_xor_sync(0xffffffffu, upper ? y[0] : y[2], 16);
+                const float k1 = (upper ? y[3] : y[1]) + __shfl_xor_sync(0xffffffffu, upper ? y[1] : y[3], 16);
+                float sum = (odd ? k1 : k0) + __shfl_xor_sync(0xffffffffu, odd ? k0 : k1, 8);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+                if ((lane & 4) == 0) sm.sums[warp][u][(lane >> 3) * 4 + (lane & 3)] = sum;
+            }
+            __syncwarp();
+            for (int o = lane; o < TT * 4; o += 32) {                  // an output a lane: (token, column)
+                const int u = o >> 2, col = o & 3, t = t0 + u;
+                const float4 part = *(const float4*)&sm.sums[warp][u][col * 4];
+                if (t < last && j0 + col < p)
+                    a.out[(size_t)t * a.ldo + (size_t)h * p + j0 + col] = ((part.x + part.y) + (part.z + part.w)) + skip * sm.v[b][u][4 * warp + col];
+            }
+            __syncwarp();
+        }
+        if (i + 1 < tiles) land(next, b ^ 1);
+    }
+    float* to = !active ? nullptr : LOCAL ? mine : (pass == REC_WHOLE || last_piece ? kept : nullptr);
+    if (to) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < R; ++i)
+                if (j0 + c < p && lane + 32 * i < n) to[(size_t)c * n + lane + 32 * i] = S[c][i];
+    }
+    if (LOCAL && j0 == 0 && lane == 0) a.scratch[(size_t)slots * hpn + (size_t)pc.slot * a.heads + h] = total;
+}
+
+// The second of the three launches: one thread per element of a request's state walks over the request's pieces.
+__global__ void recurrence_join_kernel(LlmeRecurrenceArgs a, int chunk, int slots) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.y;
+    const int pieces = (a.cu_q_lens[r + 1] - a.cu_q_lens[r] + chunk - 1) / chunk;
+    if (pieces < 2) return;
+    int base = 0;
+    for (int i = 0; i < r; ++i) {
+        const int np = (a.cu_q_lens[i + 1] - a.cu_q_lens[i] + chunk - 1) / chunk;
+        if (np > 1) base += np;
+    }
+    const size_t hpn = (size_t)a.heads * a.p * a.n, pn = (size_t)a.p * a.n;
+    const float* kept = a.state + (size_t)a.state_slots[r] * a.state_stride;
+    const float* products = a.scratch + (size_t)slots * hpn + (size_t)base * a.heads;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < hpn; e += (size_t)gridDim.x * blockDim.x) {
+        const int h = (int)(e / pn);
+        float* at = a.scratch + (size_t)base * hpn + e;
+        float S = kept[e];
+        for (int c = 0; c + 1 < pieces; ++c, at += hpn) {
+            const float added = *at;
+            *at = S;
+            S = fmaf(products[(size_t)c * a.heads + h], S, added);
+        }
+        *at = S;
+    }
+}
+
+template <bool LOCAL>
+static void recurrence_tiles(const LlmeRecurrenceArgs& a, dim3 grid, int pass, int chunk, int slots, int vec, cudaStream_t stream) {
+    const dim3 block(256);
+    if (a.n <= 32) llme_launch(recurrence_tile_kernel<1, LOCAL>, grid, block, 0, stream, a, pass, chunk, slots, vec);
+    else if (a.n <= 64) llme_launch(recurrence_tile_kernel<2, LOCAL>, grid, block, 0, stream, a, pass, chunk, slots, vec);
+    else if (a.n <= 128) llme_launch(recurrence_tile_kernel<4, LOCAL>, grid, block, 0, stream, a, pass, chunk, slots, vec);
+    else if (a.n <= 256) llme_launch(recurrence_tile_kernel<8, LOCAL>, grid, block, 0, stream, a, pass, chunk, slots, vec);
+    else llme_launch(recurrence_tile_kernel<16, LOCAL>, grid, block, 0, stream, a, pass, chunk, slots, vec);
+}
+
+// The chunk a step of `tokens` tokens whose longest request brings `max_len` is cut by, with room for `slots` piece states
+// (requests of several pieces have fewer than 2 tokens / chunk pieces together); 0: every request is walked whole.
+static int recurrence_chunk(int tokens, int max_len, long long slots) {
+    if (slots < 4 || max_len <= REC_MIN_CHUNK) return 0;
+    long long chunk = (2LL * tokens + slots - 1) / slots;
+    if (chunk < REC_MIN_CHUNK) chunk = REC_MIN_CHUNK;
+    chunk = (chunk + 31) / 32 * 32;
+    return chunk >= max_len ? 0 : (int)chunk;
+}
+
 LLME_API int llme_recurrence(const LlmeRecurrenceArgs* args, cudaStream_t stream) {
     const LlmeRecurrenceArgs& a = *args;
     if (a.requests <= 0) return 0;
@@ -193,13 +452,33 @@ LLME_API int llme_recurrence(const LlmeRecurrenceArgs* args, cudaStream_t stream
     if (a.gate == 0 ? !a.decay : (a.gate != 1 || !a.dt || !a.a_log)) LLME_REFUSE("recurrence: gate %d lacks its constants", a.gate);
     if (a.n > 512) LLME_REFUSE("recurrence: a state of %d rows per column, this build takes up to 512", a.n);
     if (a.heads > 65535 || a.requests > 65535) LLME_REFUSE("recurrence: too many heads or requests for one launch");
-    const int warps = a.p >= 8 ? 8 : a.p;
-    const dim3 grid((a.p + warps - 1) / warps, a.heads, a.requests), block(32 * warps);
-    if (a.n <= 32) llme_launch(recurrence_kernel<1>, grid, block, 0, stream, a);
-    else if (a.n <= 64) llme_launch(recurrence_kernel<2>, grid, block, 0, stream, a);
-    else if (a.n <= 128) llme_launch(recurrence_kernel<4>, grid, block, 0, stream, a);
-    else if (a.n <= 256) llme_launch(recurrence_kernel<8>, grid, block, 0, stream, a);
-    else llme_launch(recurrence_kernel<16>, grid, block, 0, stream, a);
+    if (a.max_len <= 1 || a.p < 4) {                                    // single tokens, or too few columns for four a warp
+        const int warps = a.p >= 8 ? 8 : a.p;
+        const dim3 grid((a.p + warps - 1) / warps, a.heads, a.requests), block(32 * warps);
+        if (a.n <= 32) llme_launch(recurrence_column_kernel<1>, grid, block, 0, stream, a);
+        else if (a.n <= 64) llme_launch(recurrence_column_kernel<2>, grid, block, 0, stream, a);
+        else if (a.n <= 128) llme_launch(recurrence_column_kernel<4>, grid, block, 0, stream, a);
+        else if (a.n <= 256) llme_launch(recurrence_column_kernel<8>, grid, block, 0, stream, a);
+        else llme_launch(recurrence_column_kernel<16>, grid, block, 0, stream, a);
+        LLME_LAUNCH_STATUS();
+    }
+    const long long hpn = (long long)a.heads * a.p * a.n;
+    const long long slots = a.scratch ? a.scratch_floats / (hpn + a.heads) : 0;
+    const int chunk = recurrence_chunk(a.tokens, a.max_len, slots);
+    // 16-byte copies where every row of q and k starts on such a boundary
+    const int vec = ((uintptr_t)a.q % 16 == 0 && (uintptr_t)a.k % 16 == 0 && a.ldq % 4 == 0 && a.ldk % 4 == 0 && a.n % 4 == 0) ? 1 : 0;
+    dim3 grid((a.p + REC_COLUMNS - 1) / REC_COLUMNS, a.heads, a.requests);
+    if (!chunk) {
+        recurrence_tiles<false>(a, grid, REC_WHOLE, 0, 0, vec, stream);
+        LLME_LAUNCH_STATUS();
+    }
+    const long long most = (long long)a.tokens / chunk + a.requests;     // no step has more pieces
+    if (most > 65535) LLME_REFUSE("recurrence: %lld pieces are too many for one launch", most);
+    grid.z = (unsigned)most;
+    recurrence_tiles<true>(a, grid, REC_LOCAL, chunk, (int)slots, vec, stream);
+    const long long blocks = (hpn + 255) / 256;
+    llme_launch(recurrence_join_kernel, dim3((unsigned)(blocks < 1024 ? blocks : 1024), a.requests), dim3(256), 0, stream, a, chunk, (int)slots);
+    recurrence_tiles<false>(a, grid, REC_FROM_START, chunk, (int)slots, vec, stream);
     LLME_LAUNCH_STATUS();
 }
 

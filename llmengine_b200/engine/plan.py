@@ -207,13 +207,14 @@ class Plan:
                   inv_freq=inv_freq)
 
     def recurrence(self, *, q, k, v, state, out, heads: int, n: int, p: int, qk_groups: int, decay=None, dt=None, dt_bias=None,
-                   a_log=None, skip=None) -> None:
+                   a_log=None, skip=None, scratch=None) -> None:
         """Per request and head, over the request's tokens in order: S_t = a_t S_(t-1) + s_t k_t v_t^T (S is n x p),
         y_t = S_t^T q_t + skip_h v_t.  With `decay` [H]: a_t = decay_h, s_t = 1.  With `dt` [T, H], `dt_bias` and `a_log`
         [H]: d = softplus(dt + dt_bias), a_t = exp(-exp(a_log_h) d), s_t = d.  q, k [T, qk_groups * n] and out [T, H p] are
-        32-bit; head h reads group h // (H / qk_groups).  `state` [slots, H, p, n] 32-bit goes from step to step."""
+        32-bit; head h reads group h // (H / qk_groups).  `state` [slots, H, p, n] 32-bit goes from step to step.  With `scratch`
+        (32-bit, a few states large) a long portion is cut into pieces that run side by side."""
         self._add("recurrence", q=q, k=k, v=v, state=state, out=out, heads=int(heads), n=int(n), p=int(p), qk_groups=int(qk_groups),
-                  decay=decay, dt=dt, dt_bias=dt_bias, a_log=a_log, skip=skip)
+                  decay=decay, dt=dt, dt_bias=dt_bias, a_log=a_log, skip=skip, scratch=scratch)
 
     def gated_norm(self, *, y, gate, weight, out, group: int, gate_first: bool, eps: float, scale: float = 1.0) -> None:
         """RMS norm of y [T, C] (32-bit) in groups of `group` columns, with g = silu(gate): `gate_first`: u = y g,

@@ -276,6 +276,7 @@ typedef struct LlmeRecurrenceOp {
     float* state; long long state_stride;
     float* out; long long ldo;
     int heads, n, p;
+    float* scratch; long long scratch_floats;                /* lets long portions run in pieces side by side, or NULL */
 } LlmeRecurrenceOp;
 
 /* RMS norm in groups of `group` columns with a silu gate: gate_first 1: u = y silu(g), out = u / rms(u) * weight; 0:

@@ -176,7 +176,7 @@ class RecurrenceOp(Structure):
                 ("v", c_void_p), ("ldv", c_longlong), ("v_dtype", c_int), ("gate", c_int), ("decay", c_void_p),
                 ("dt", c_void_p), ("lddt", c_longlong), ("dt_dtype", c_int), ("dt_bias", c_void_p), ("a_log", c_void_p),
                 ("skip", c_void_p), ("state", c_void_p), ("state_stride", c_longlong), ("out", c_void_p), ("ldo", c_longlong),
-                ("heads", c_int), ("n", c_int), ("p", c_int)]
+                ("heads", c_int), ("n", c_int), ("p", c_int), ("scratch", c_void_p), ("scratch_floats", c_longlong)]
 
 
 class GatedNormOp(Structure):
@@ -420,14 +420,16 @@ def records(op, keep: List[Any]):
         assert q.dtype == kk.dtype == out.dtype == torch.float32 and q.stride(1) == kk.stride(1) == v.stride(1) == out.stride(1) == 1
         assert q.shape[1] == kk.shape[1] == G * n and v.shape[1] == out.shape[1] == H * p and H % G == 0
         assert _state(st) and tuple(st.shape[1:]) == (H, p, n)
-        dt = a.get("dt")
+        dt, scratch = a.get("dt"), a.get("scratch")
+        assert scratch is None or (scratch.dtype == torch.float32 and scratch.is_contiguous())
         assert dt is None or (dt.stride(1) == 1 and dt.shape[1] == H)
         for t in ("decay", "dt_bias", "a_log", "skip"):
             assert _f32(a.get(t), H)
         return OP_RECURRENCE, RecurrenceOp(q.data_ptr(), kk.data_ptr(), q.stride(0), kk.stride(0), G, v.data_ptr(), v.stride(0), code(v.dtype),
                                            0 if dt is None else 1, ptr(a.get("decay")), ptr(dt), dt.stride(0) if dt is not None else 0,
                                            code(dt.dtype) if dt is not None else 0, ptr(a.get("dt_bias")), ptr(a.get("a_log")),
-                                           ptr(a.get("skip")), st.data_ptr(), st.stride(0), out.data_ptr(), out.stride(0), H, n, p)
+                                           ptr(a.get("skip")), st.data_ptr(), st.stride(0), out.data_ptr(), out.stride(0), H, n, p,
+                                           ptr(scratch), scratch.numel() if scratch is not None else 0)
     if k == "gated_norm":
         y, g, w, out = a["y"], a["gate"], a["weight"], a["out"]
         cols = y.shape[1]

@@ -266,6 +266,16 @@ class Runtime:
             return None
         return self.buffer("attention_scratch", 1, n, torch.float32, exact=True, zero=True).view(-1)
 
+    def recurrence_scratch(self, heads: int, p: int, n: int) -> Optional[torch.Tensor]:
+        """Room for the states that the pieces of long portions start from (one buffer for all layers, as large as the
+        largest state among them needs): a step of T tokens cut every c tokens has fewer than 2 T / c pieces in requests
+        of several, each with a [heads, p, n] state and a product of decays per head.  Up to 64 pieces of 64 tokens or more."""
+        if self.max_tokens <= 64 or self.device.type != "cuda":
+            return None
+        pieces = min(64, max(4, 2 * ((self.max_tokens + 63) // 64)))
+        self._recurrence_scratch_floats = max(getattr(self, "_recurrence_scratch_floats", 0), pieces * heads * (p * n + 1))
+        return self.buffer("recurrence_scratch", 1, self._recurrence_scratch_floats, torch.float32, exact=True).view(-1)
+
     def latent_scratch(self, num_heads: int, kv_rank: int) -> Optional[torch.Tensor]:
         """Scratch memory of the latent attention whose requests are cut into several key ranges (one buffer for all
         layers, as large as the widest of them needs)."""

@@ -77,7 +77,8 @@ class StateSpaceMixer(Part):
         y = rt.workspace("ssm_y", inner, torch.float32)
         plan.recurrence(q=xbc[:, inner + bc:], k=xbc[:, inner:inner + bc], v=xbc[:, :inner], state=cache.states["state"], out=y,
                         heads=self.nh, n=self.n, p=self.p, qk_groups=self.groups, dt=proj[:, inner + self.conv_channels:],
-                        dt_bias=self.dt_bias, a_log=self.a_log, skip=self.skip)
+                        dt_bias=self.dt_bias, a_log=self.a_log, skip=self.skip,
+                        scratch=rt.recurrence_scratch(self.nh, self.p, self.n))
         gated = rt.workspace("ssm_gated", inner, rt.dtype)
         plan.gated_norm(y=y, gate=proj[:, :inner], weight=self.norm_w, out=gated, group=inner // self.norm_groups, gate_first=True,
                         eps=self.eps)
@@ -137,7 +138,7 @@ class Retention(Part):
                     dim=self.dk, rot_dims=pos.dims if pos is not None else 0, inv_freq=pos.frequencies() if pos is not None else None)
         o = rt.workspace("retention_o", hs, torch.float32)
         plan.recurrence(q=q32, k=k32, v=proj[:, 2 * qs:2 * qs + hs], state=cache.states["state"], out=o, heads=self.nh, n=self.dk,
-                        p=self.dv, qk_groups=self.nh, decay=self.decay)
+                        p=self.dv, qk_groups=self.nh, decay=self.decay, scratch=rt.recurrence_scratch(self.nh, self.dv, self.dk))
         plan.gated_norm(y=o, gate=proj[:, 2 * qs + hs:2 * qs + 2 * hs], weight=None, out=out, group=self.dv, gate_first=False,
                         eps=self.eps, scale=scale)
 

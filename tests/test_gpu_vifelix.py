@@ -117,23 +117,37 @@ def _recurrence_plain(q, k, v, decay, step, skip, S):
 def test_recurrence_kernel(gated, H, G, n, p):
     """Both forms of the recurrence (a fixed decay per head; decay and step from every token's dt), requests of unequal
     length in two steps, a request that starts from a state left by the step before, heads sharing q and k by groups."""
+    _check_recurrence(gated, H, G, n, p, [37, 1, 12], [30, 0, 11], [1, 3, 0], 0, 2e-5)
+
+
+@pytest.mark.parametrize("H,G,n,p,room", [(2, 1, 8, 16, 64), (3, 3, 6, 5, 7), (2, 2, 128, 64, 20), (1, 1, 40, 9, 4)])
+@pytest.mark.parametrize("gated", [False, True])
+def test_recurrence_in_pieces(gated, H, G, n, p, room):
+    """Long portions cut into pieces that run side by side: requests of one piece, of exactly one and two pieces, one token
+    more and one fewer, beside single tokens; the second step starts every request from the state the first one left.  With
+    little room the pieces grow longer than the shortest the kernel cuts (64 tokens)."""
+    _check_recurrence(gated, H, G, n, p, [431, 1, 128, 65, 140, 64, 2], [300, 0, 64, 0, 11, 63, 1], [1, 3, 0, 5, 2, 6, 4],
+                      room * H * (p * n + 1), 1e-4)
+
+
+def _check_recurrence(gated, H, G, n, p, lens, cuts, slots, scratch_floats, tol):
     ops = _ops()
     g = torch.Generator().manual_seed(n + p)
-    lens, cuts, slots = [37, 1, 12], [30, 0, 11], [1, 3, 0]
+    scratch = torch.full((scratch_floats,), float("nan"), device=DEV) if scratch_floats else None
     mk = lambda *s: torch.randn(*s, generator=g)
     q, k, v = [mk(L, G * n) for L in lens], [mk(L, G * n) / math.sqrt(n) for L in lens], [mk(L, H * p) for L in lens]
     dt = [mk(L, H).to(torch.bfloat16) for L in lens]
     dt_bias, a_log, skip = mk(H) - 1, mk(H) * 0.5, mk(H)
     decay = torch.rand(H, generator=g) * 0.3 + 0.7
-    state = torch.zeros(4, H, p, n, device=DEV)
+    state = torch.zeros(max(slots) + 2, H, p, n, device=DEV)
     got = [[] for _ in lens]
     for step in range(2):
-        spans = [(r, 0, cuts[r]) if step == 0 else (r, cuts[r], lens[r]) for r in range(3)]
+        spans = [(r, 0, cuts[r]) if step == 0 else (r, cuts[r], lens[r]) for r in range(len(lens))]
         spans = [s for s in spans if s[2] > s[1]]
         cat = lambda xs: torch.cat([xs[r][a:b] for r, a, b in spans]).to(DEV)
         out = torch.zeros(sum(b - a for _, a, b in spans), H * p, device=DEV)
         kw = dict(dt=cat(dt), dt_bias=dt_bias.to(DEV), a_log=a_log.to(DEV), skip=skip.to(DEV)) if gated else dict(decay=decay.to(DEV))
-        _run(ops, lambda pl: pl.recurrence(q=cat(q), k=cat(k), v=cat(v), state=state, out=out, heads=H, n=n, p=p, qk_groups=G, **kw),
+        _run(ops, lambda pl: pl.recurrence(q=cat(q), k=cat(k), v=cat(v), state=state, out=out, heads=H, n=n, p=p, qk_groups=G, scratch=scratch, **kw),
              _batch([b - a for _, a, b in spans], [slots[r] for r, _, _ in spans]))
         at = 0
         for r, a, b in spans:
@@ -151,9 +165,9 @@ def test_recurrence_kernel(gated, H, G, n, p):
             want, S = _recurrence_plain(q[r][:, gq * n:(gq + 1) * n], k[r][:, gq * n:(gq + 1) * n], v[r][:, h * p:(h + 1) * p], dc, st,
                                         skip[h] if gated else 0.0, torch.zeros(n, p))
             scale = max(1.0, float(want.abs().max()))
-            assert float((y[:, h * p:(h + 1) * p] - want).abs().max()) < 2e-5 * scale, (r, h)
-            assert float((state[slots[r], h].cpu() - S.t()).abs().max()) < 2e-5 * max(1.0, float(S.abs().max()))
-    assert float(state[2].abs().max()) == 0.0
+            assert float((y[:, h * p:(h + 1) * p] - want).abs().max()) < tol * scale, (r, h)
+            assert float((state[slots[r], h].cpu() - S.t()).abs().max()) < tol * max(1.0, float(S.abs().max()))
+    assert float(state[max(slots) + 1].abs().max()) == 0.0
 
 
 @pytest.mark.parametrize("cols,group", [(64, 16), (30, 30), (36, 6), (512, 128)])
@@ -314,8 +328,9 @@ def test_a_key_that_stands_out_at_the_window_s_edge(tmp_path, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_token_far_back_that_only_the_states_remember(tmp_path, dtype):
     """A model whose window is 4 tokens, whose retention never forgets (decay 1) and whose state space forgets slowly: changing
-    the FIRST token of a prompt of 300 still moves the last logits far beyond the tolerance, so a state that is lost, zeroed
-    or taken from another slot on the way (portions, single tokens, slots used again) would show."""
+    the FIRST token of a prompt of 300 still moves the last logits far beyond the 32-bit tolerance, so a state that is lost,
+    zeroed or taken from another slot on the way (portions, single tokens, slots used again) would show there; the bfloat16
+    run replays the same schedules."""
     cfg = model(45, 48, 1e-5, 5.0, [
         layer("parallel", parallel(left(2, 1, 16, 0.3, 4, base=100.0), right(2, 16, 16, (1.0, 0.999), base=1e6), 0.3, 1.5), None),
         layer("mamba2", ssm(3, 16, 16, 1, 2, 3)),
@@ -329,7 +344,8 @@ def test_a_token_far_back_that_only_the_states_remember(tmp_path, dtype):
     plain = PlainVifelix(d)
     other = list(reqs["r0"])
     other[0] = (other[0] + 1) % 45
-    assert float((plain.logits(other)[-1] - ref["r0"][-1]).abs().max()) > 5 * tol
+    if dtype == "float32":      # bfloat16 rounding of 300 tokens' sums moves these logits more than the first token does
+        assert float((plain.logits(other)[-1] - ref["r0"][-1]).abs().max()) > 5 * tol
     for what, steps in schedules(reqs, tail=40).items():
         eng = engine_for(d, dtype, max_live_tokens(steps, 64), page_size=16, max_requests=4, max_model_len=512)
         compare(replay(eng, steps, poison=True), ref, tol, f"far/{dtype}/{what}")
