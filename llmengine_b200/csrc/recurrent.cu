@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(256) recurrence_column_kernel(LlmeRecurrenceAr
 }
 
 // Portions of prompts: a block of eight warps takes 32 neighbouring columns of one (request or piece of it, head), four a warp
-// (lane l holds S[l + 32 i] of each of its four).  The block brings q and k of a few tokens at a time into shared memory with
+// (lane l holds S[R l + i], i < R, of each of its four, so its q and k come from shared memory in one piece).  The block brings q and k of a few tokens at a time into shared memory with
 // asynchronous copies, and v, the steps and the decays beside them, while it works on the tokens before: every warp of the
 // block needs the same q and k, and no token's operands come from global memory when they are due.  A token costs a warp 4 R
 // multiply-adds for the update, 4 R for the output, and six exchanges that sum the four columns over the lanes (each lane
@@ -221,6 +221,25 @@ __device__ __forceinline__ void copy_async_16(float* dst, const float* src) {
 }
 __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
+// Two 32-bit values in one 64-bit register and the packed multiply-add on both (each half rounds as fmaf does).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 template <int R> struct RecTile {
     static constexpr int TOKENS = R <= 4 ? 16 : (R == 8 ? 8 : 4);       // tokens in shared memory at a time, twice
     static constexpr int ROW = 32 * R;                                   // n rounded up
@@ -253,12 +272,15 @@ __global__ void __launch_bounds__(256, R <= 4 ? 3 : 1) recurrence_tile_kernel(Ll
     float* kept = a.state + (size_t)a.state_slots[pc.r] * a.state_stride + column;
     float* mine = pc.pieces > 1 ? a.scratch + (size_t)pc.slot * hpn + column : nullptr;
     const float* from = LOCAL || !active ? nullptr : (mine ? mine : kept);
-    float S[4][R];
+    f32x2 S[2][R];                                                     // columns 0 | 1 and 2 | 3, packed
 #pragma unroll
-    for (int c = 0; c < 4; ++c)
+    for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int i = 0; i < R; ++i)
-            S[c][i] = from && j0 + c < p && lane + 32 * i < n ? from[(size_t)c * n + lane + 32 * i] : 0.0f;
+        for (int i = 0; i < R; ++i) {
+            const bool row = from && lane * R + i < n;
+            S[c][i] = pack2(row && j0 + 2 * c < p ? from[(size_t)(2 * c) * n + lane * R + i] : 0.0f,
+                            row && j0 + 2 * c + 1 < p ? from[(size_t)(2 * c + 1) * n + lane * R + i] : 0.0f);
+        }
     const int g = h / (a.heads / a.qk_groups);
     const float fixed = a.gate == 0 ? a.decay[h] : 0.0f;
     const float rate = a.gate == 1 ? -expf(a.a_log[h]) : 0.0f;
@@ -336,35 +358,39 @@ __global__ void __launch_bounds__(256, R <= 4 ? 3 : 1) recurrence_tile_kernel(Ll
         const int next = first + (LOCAL ? tile - 1 : tile + 1) * TT;
         if (i + 1 < tiles) fetch(next, b ^ 1);
         if (active && LOCAL) {
-#pragma unroll 4
+#pragma unroll
             for (int u = TT - 1; u >= 0; --u) {
                 const float w = sm.step[b][u] * total;
                 const float4 v4 = *(const float4*)&sm.v[b][u][4 * warp];
-                const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+                const f32x2 v01 = pack2(v4.x, v4.y), v23 = pack2(v4.z, v4.w);
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
-                    const float kw = w * sm.k[b][u][lane + 32 * r];
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) S[c][r] = fmaf(kw, v[c], S[c][r]);
+                    const float kw = w * sm.k[b][u][lane * R + r];
+                    const f32x2 kw2 = pack2(kw, kw);
+                    S[0][r] = fma2(kw2, v01, S[0][r]);
+                    S[1][r] = fma2(kw2, v23, S[1][r]);
                 }
                 total *= sm.decay[b][u];
             }
         } else if (active) {
-#pragma unroll 4
+#pragma unroll
             for (int u = 0; u < TT; ++u) {
                 const float step = sm.step[b][u], decay = sm.decay[b][u];
                 const float4 v4 = *(const float4*)&sm.v[b][u][4 * warp];
-                const float v[4] = {v4.x, v4.y, v4.z, v4.w};
-                float y[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                const f32x2 v01 = pack2(v4.x, v4.y), v23 = pack2(v4.z, v4.w), decay2 = pack2(decay, decay);
+                f32x2 y01 = pack2(0.0f, 0.0f), y23 = y01;
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
-                    const float qi = sm.q[b][u][lane + 32 * r], ks = step * sm.k[b][u][lane + 32 * r];
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        S[c][r] = fmaf(decay, S[c][r], ks * v[c]);
-                        y[c] = fmaf(S[c][r], qi, y[c]);
-                    }
+                    const float qi = sm.q[b][u][lane * R + r], ks = step * sm.k[b][u][lane * R + r];
+                    const f32x2 qi2 = pack2(qi, qi), ks2 = pack2(ks, ks);
+                    S[0][r] = fma2(decay2, S[0][r], mul2(ks2, v01));      // S = a S + (s k) v, as the single-token kernel rounds it
+                    S[1][r] = fma2(decay2, S[1][r], mul2(ks2, v23));
+                    y01 = fma2(S[0][r], qi2, y01);
+                    y23 = fma2(S[1][r], qi2, y23);
                 }
+                float y[4];
+                unpack2(y01, y[0], y[1]);
+                unpack2(y23, y[2], y[3]);
                 // lanes 16..31 take over columns 2 and 3, then of each half the lanes with bit 3 set the odd column; after one
                 // more exchange lanes 8 c .. 8 c + 3 hold four parts of column c, which go to shared memory
                 const bool upper = lane & 16, odd = lane & 8;
@@ -388,10 +414,14 @@ __global__ void __launch_bounds__(256, R <= 4 ? 3 : 1) recurrence_tile_kernel(Ll
     float* to = !active ? nullptr : LOCAL ? mine : (pass == REC_WHOLE || last_piece ? kept : nullptr);
     if (to) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
-            for (int i = 0; i < R; ++i)
-                if (j0 + c < p && lane + 32 * i < n) to[(size_t)c * n + lane + 32 * i] = S[c][i];
+            for (int i = 0; i < R; ++i) {
+                float lo, hi;
+                unpack2(S[c][i], lo, hi);
+                if (j0 + 2 * c < p && lane * R + i < n) to[(size_t)(2 * c) * n + lane * R + i] = lo;
+                if (j0 + 2 * c + 1 < p && lane * R + i < n) to[(size_t)(2 * c + 1) * n + lane * R + i] = hi;
+            }
     }
     if (LOCAL && j0 == 0 && lane == 0) a.scratch[(size_t)slots * hpn + (size_t)pc.slot * a.heads + h] = total;
 }
@@ -415,7 +445,21 @@ __global__ void recurrence_join_kernel(LlmeRecurrenceArgs a, int chunk, int slot
         const int h = (int)(e / pn);
         float* at = a.scratch + (size_t)base * hpn + e;
         float S = kept[e];
-        for (int c = 0; c + 1 < pieces; ++c, at += hpn) {
+        int c = 0;
+        for (; c + 4 < pieces; c += 4, at += 4 * hpn) {                  // four pieces' loads are on their way at a time
+            float added[4], product[4];
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                added[m] = at[(size_t)m * hpn];
+                product[m] = products[(size_t)(c + m) * a.heads + h];
+            }
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                at[(size_t)m * hpn] = S;
+                S = fmaf(product[m], S, added[m]);
+            }
+        }
+        for (; c + 1 < pieces; ++c, at += hpn) {
             const float added = *at;
             *at = S;
             S = fmaf(products[(size_t)c * a.heads + h], S, added);
