@@ -86,8 +86,9 @@ LLME_API int llme_short_conv(const LlmeShortConvArgs* args, int update, cudaStre
     if (update) {
         if (a.taps > 1) llme_launch(short_conv_state_kernel, dim3(a.requests, pieces), dim3(threads), 0, stream, a);
     } else {
-        const int wanted = (592 + a.tokens - 1) / a.tokens;
-        if (pieces > wanted) pieces = wanted;
+        // a thread takes up to four channels of its token, more where the step has too few tokens to fill the GPU otherwise
+        const int fill = (592 + a.tokens - 1) / a.tokens, quarter = (pieces + 3) / 4;
+        pieces = min(pieces, max(fill, quarter));
         llme_launch(short_conv_kernel, dim3(a.tokens, pieces < 1 ? 1 : pieces), dim3(threads), 0, stream, a);
     }
     LLME_LAUNCH_STATUS();
