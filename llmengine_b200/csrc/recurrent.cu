@@ -50,6 +50,41 @@ __global__ void short_conv_kernel(LlmeShortConvArgs a) {
     }
 }
 
+// The same for a number of taps known when compiling: a thread takes four channels at once, all their inputs and weights on
+// their way before the first sum (the sums in the order of the kernel above).
+template <int K>
+__global__ void short_conv_taps_kernel(LlmeShortConvArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int r = row_of_token(a.cu_q_lens, a.requests, t);
+    const int i = t - a.cu_q_lens[r];
+    const float* st = a.state + (size_t)a.state_slots[r] * a.state_stride;
+    const int stride = gridDim.y * blockDim.x;
+    for (int c0 = blockIdx.y * blockDim.x + threadIdx.x; c0 < a.channels; c0 += 4 * stride) {
+        float x[4][K], w[4][K], y[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const int c = c0 + m * stride;
+            const bool ok = c < a.channels;
+            y[m] = ok && a.bias ? a.bias[c] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < K; ++j) {
+                const int src = i - j;
+                x[m][j] = !ok ? 0.0f : src >= 0 ? load_as_f32(a.x, a.x_dtype, (size_t)(t - j) * a.ldx + c) : st[(size_t)(K - 1 + src) * a.channels + c];
+                w[m][j] = ok ? a.w[(size_t)c * K + (K - 1 - j)] : 0.0f;
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const int c = c0 + m * stride;
+#pragma unroll
+            for (int j = K - 1; j >= 0; --j) y[m] = fmaf(w[m][j], x[m][j], y[m]);
+            if (c < a.channels) a.out[(size_t)t * a.ldo + c] = a.act == 1 ? silu32(y[m]) : y[m];
+        }
+    }
+}
+
 __global__ void short_conv_state_kernel(LlmeShortConvArgs a) {
     pdl_launch_dependents();
     pdl_wait();
@@ -89,7 +124,11 @@ LLME_API int llme_short_conv(const LlmeShortConvArgs* args, int update, cudaStre
         // a thread takes up to four channels of its token, more where the step has too few tokens to fill the GPU otherwise
         const int fill = (592 + a.tokens - 1) / a.tokens, quarter = (pieces + 3) / 4;
         pieces = min(pieces, max(fill, quarter));
-        llme_launch(short_conv_kernel, dim3(a.tokens, pieces < 1 ? 1 : pieces), dim3(threads), 0, stream, a);
+        const dim3 grid(a.tokens, pieces < 1 ? 1 : pieces);
+        if (a.taps == 4) llme_launch(short_conv_taps_kernel<4>, grid, dim3(threads), 0, stream, a);
+        else if (a.taps == 3) llme_launch(short_conv_taps_kernel<3>, grid, dim3(threads), 0, stream, a);
+        else if (a.taps == 2) llme_launch(short_conv_taps_kernel<2>, grid, dim3(threads), 0, stream, a);
+        else llme_launch(short_conv_kernel, grid, dim3(threads), 0, stream, a);
     }
     LLME_LAUNCH_STATUS();
 }

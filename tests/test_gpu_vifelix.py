@@ -53,7 +53,7 @@ def _batch(q_lens, slots, positions=None):
 
 
 # ----------------------------------------------------------------------------- single kernels
-@pytest.mark.parametrize("C,K", [(40, 4), (7, 1), (300, 5), (64, 2)])
+@pytest.mark.parametrize("C,K", [(40, 4), (7, 1), (300, 5), (64, 2), (50, 3), (1100, 4)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_short_convolution_kernel(dtype, C, K):
     """Three requests of unequal length in slots that are not in order, cut into two steps at places of their own (one
