@@ -85,6 +85,89 @@ __global__ void short_conv_taps_kernel(LlmeShortConvArgs a) {
     }
 }
 
+// Prompt portions whose rows allow loads of four channels at once: a thread owns four neighbouring channels and walks over
+// CONV_TOKENS tokens of the step, keeping the K - 1 inputs before the present one in registers, so an input is read once (and
+// once more by the block that takes the next tokens); where a request begins inside the walk the window is read anew (from the
+// request's state).  The sums are those of the kernel above, in its order.
+constexpr int CONV_TOKENS = 16;
+
+template <typename T> __device__ __forceinline__ void load_four(const T* p, float (&v)[4]);
+template <> __device__ __forceinline__ void load_four<float>(const float* p, float (&v)[4]) {
+    const float4 f = *(const float4*)p;
+    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+}
+template <> __device__ __forceinline__ void load_four<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 raw = *(const uint2*)p;
+    const __nv_bfloat162 lo = *(const __nv_bfloat162*)&raw.x, hi = *(const __nv_bfloat162*)&raw.y;
+    v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
+}
+
+template <int K, typename T>
+__global__ void __launch_bounds__(128) short_conv_walk_kernel(LlmeShortConvArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (c >= a.channels) return;
+    const int t0 = blockIdx.x * CONV_TOKENS, t1 = min(a.tokens, t0 + CONV_TOKENS);
+    float w[4][K], bias[4];
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        bias[m] = a.bias ? a.bias[c + m] : 0.0f;
+#pragma unroll
+        for (int j = 0; j < K; ++j) w[m][j] = a.w[(size_t)(c + m) * K + (K - 1 - j)];      // w[m][j] meets the input j tokens back
+    }
+    const T* x = (const T*)a.x;
+    float present[CONV_TOKENS][4];                                      // all of the walk's inputs are on their way at once
+#pragma unroll
+    for (int u = 0; u < CONV_TOKENS; ++u)
+        if (t0 + u < t1) load_four<T>(x + (size_t)(t0 + u) * a.ldx + c, present[u]);
+    float back[K][4];                                                   // back[j]: the input j tokens before the present one
+    int r = row_of_token(a.cu_q_lens, a.requests, t0), begin = a.cu_q_lens[r], end = a.cu_q_lens[r + 1];
+    bool fresh = true;
+#pragma unroll
+    for (int u = 0; u < CONV_TOKENS; ++u) {
+        const int t = t0 + u;
+        if (t >= t1) break;
+        while (t >= end) {                                              // the next request that has tokens
+            ++r;
+            begin = end;
+            end = a.cu_q_lens[r + 1];
+            fresh = true;
+        }
+        const int i = t - begin;
+        if (fresh) {
+            const float* st = a.state + (size_t)a.state_slots[r] * a.state_stride;
+#pragma unroll
+            for (int j = 1; j < K; ++j) {
+                if (i - j >= 0) load_four<T>(x + (size_t)(t - j) * a.ldx + c, back[j]);
+                else load_four<float>(st + (size_t)(K - 1 + i - j) * a.channels + c, back[j]);
+            }
+            fresh = false;
+        }
+        float y[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            back[0][m] = present[u][m];
+            y[m] = bias[m];
+#pragma unroll
+            for (int j = K - 1; j >= 0; --j) y[m] = fmaf(w[m][j], back[j][m], y[m]);
+            if (a.act == 1) y[m] = silu32(y[m]);
+        }
+        *(float4*)(a.out + (size_t)t * a.ldo + c) = make_float4(y[0], y[1], y[2], y[3]);
+#pragma unroll
+        for (int j = K - 1; j > 0; --j)
+#pragma unroll
+            for (int m = 0; m < 4; ++m) back[j][m] = back[j - 1][m];
+    }
+}
+
+template <int K>
+static void short_conv_walk(const LlmeShortConvArgs& a, cudaStream_t stream) {
+    const dim3 grid((a.tokens + CONV_TOKENS - 1) / CONV_TOKENS, (a.channels / 4 + 127) / 128), block(128);
+    if (a.x_dtype == LLME_F32) llme_launch(short_conv_walk_kernel<K, float>, grid, block, 0, stream, a);
+    else llme_launch(short_conv_walk_kernel<K, __nv_bfloat16>, grid, block, 0, stream, a);
+}
+
 __global__ void short_conv_state_kernel(LlmeShortConvArgs a) {
     pdl_launch_dependents();
     pdl_wait();
@@ -124,6 +207,16 @@ LLME_API int llme_short_conv(const LlmeShortConvArgs* args, int update, cudaStre
         // a thread takes up to four channels of its token, more where the step has too few tokens to fill the GPU otherwise
         const int fill = (592 + a.tokens - 1) / a.tokens, quarter = (pieces + 3) / 4;
         pieces = min(pieces, max(fill, quarter));
+        // rows of x, of the output and of the state that start on 16 bytes (8 for bf16 inputs), channels in fours
+        const size_t el = a.x_dtype == LLME_F32 ? 4 : 2;
+        const bool fours = a.channels % 4 == 0 && (uintptr_t)a.x % (4 * el) == 0 && a.ldx % 4 == 0 && (uintptr_t)a.out % 16 == 0 &&
+                           a.ldo % 4 == 0 && (uintptr_t)a.state % 16 == 0 && a.state_stride % 4 == 0;
+        if (fours && a.tokens >= 8 * CONV_TOKENS && a.taps >= 2 && a.taps <= 4) {
+            if (a.taps == 4) short_conv_walk<4>(a, stream);
+            else if (a.taps == 3) short_conv_walk<3>(a, stream);
+            else short_conv_walk<2>(a, stream);
+            LLME_LAUNCH_STATUS();
+        }
         const dim3 grid(a.tokens, pieces < 1 ? 1 : pieces);
         if (a.taps == 4) llme_launch(short_conv_taps_kernel<4>, grid, dim3(threads), 0, stream, a);
         else if (a.taps == 3) llme_launch(short_conv_taps_kernel<3>, grid, dim3(threads), 0, stream, a);

@@ -62,18 +62,18 @@ def torisun_shape(layers: int, width: int, heads: int, kv_heads: int, ff: int, e
 
 def vifelix_shape(width: int, heads: int, kv_heads: int, ff: int, ssm_heads: int, retention_heads: int, window: int = 1024,
                   dim: int = 128, state: int = 128, vocab: int = 32768) -> Dict[str, Any]:
-    """Six layers: state-space layers without feed-forward around two parallel layers (window attention beside retention)
+    """Six layers: four state-space layers without feed-forward and two parallel layers (window attention beside retention)
     with one.  The state-space mixer is twice the width inside, in heads of 64."""
     mamba = {"type": "mamba2", "mlp": None,
              "mixer": {"heads": ssm_heads, "vdim": 64, "state": state, "groups": 8, "conv": 4, "norm_groups": 8}}
     par = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff}, "mixer": {
         "left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
-                 "rot": {"base": 500000.0, "dims": dim // 2}},
-        "right": {"heads": retention_heads, "dim": dim, "vdim": dim, "decay": [1.0 - 2.0 ** (-5 - i % 6) for i in range(retention_heads)],
-                  "rot": {"base": 1000000.0, "dims": dim}},
-        "left_scale": 1.2, "right_scale": 1.1}}
+                 "rot": {"base": 10000.0, "dims": dim // 2}},
+        "right": {"heads": retention_heads, "dim": dim, "vdim": dim, "decay": [1.0 - 0.04 / (1 + i) for i in range(retention_heads)],
+                  "rot": {"base": 100000.0, "dims": dim}},
+        "left_scale": 0.9, "right_scale": 0.7}}
     return {"architecture": "Vifelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": width ** 0.5},
-            "layers": [mamba, par, mamba, mamba, par, mamba]}
+            "layers": [mamba, mamba, par, mamba, mamba, par]}
 
 
 # 32-bit multiply-adds outside the tensor cores: 148 SMs x 128 lanes x 2 x 1.965 GHz (nominal), the compute ceiling of a

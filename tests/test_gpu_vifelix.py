@@ -58,30 +58,42 @@ def _batch(q_lens, slots, positions=None):
 def test_short_convolution_kernel(dtype, C, K):
     """Three requests of unequal length in slots that are not in order, cut into two steps at places of their own (one
     request brings a single token in the second step, one nothing in the first): the state carries the last K - 1 inputs."""
+    _check_short_convolution(dtype, C, K, [9, 1, 6], [4, 0, 5], 3)
+
+
+@pytest.mark.parametrize("C,K", [(64, 4), (40, 3), (520, 2), (36, 5)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_short_convolution_over_long_portions(dtype, C, K):
+    """Steps of more than a hundred tokens, rows that start on 16 bytes: the kernel in which a thread walks over 16 tokens
+    with four channels; requests begin and end inside a walk, one brings a single token, one continues from its state."""
+    _check_short_convolution(dtype, C, K, [150, 1, 37, 203], [90, 0, 36, 47], 4)
+
+
+def _check_short_convolution(dtype, C, K, lens, cuts, pad):
     ops = _ops()
     g = torch.Generator().manual_seed(C + K)
-    lens, cuts, slots = [9, 1, 6], [4, 0, 5], [3, 0, 2]
+    slots = [3, 0, 2, 4][:len(lens)]
     xs = [torch.randn(n, C, generator=g).to(dtype) for n in lens]
     w, b = torch.randn(C, K, generator=g), torch.randn(C, generator=g)
-    state = torch.zeros(5, max(K - 1, 1), C, device=DEV)
+    state = torch.zeros(6, max(K - 1, 1), C, device=DEV)
     state[1] = float("nan")                                        # a slot nobody uses is never touched
     got = [[] for _ in lens]
     for step in range(2):
-        spans = [(r, 0, cuts[r]) if step == 0 else (r, cuts[r], lens[r]) for r in range(3)]
+        spans = [(r, 0, cuts[r]) if step == 0 else (r, cuts[r], lens[r]) for r in range(len(lens))]
         spans = [s for s in spans if s[2] > s[1]]
-        wide = torch.cat([torch.zeros(sum(b_ - a for _, a, b_ in spans), 3, dtype=dtype), torch.cat([xs[r][a:b_] for r, a, b_ in spans])], 1).to(DEV)
+        wide = torch.cat([torch.zeros(sum(b_ - a for _, a, b_ in spans), pad, dtype=dtype), torch.cat([xs[r][a:b_] for r, a, b_ in spans])], 1).to(DEV)
         out = torch.zeros(wide.shape[0] + 1, C, device=DEV)
-        _run(ops, lambda p: p.short_conv(x=wide[:, 3:], w=w.to(DEV), bias=b.to(DEV), state=state, out=out, act="silu"),
+        _run(ops, lambda p: p.short_conv(x=wide[:, pad:], w=w.to(DEV), bias=b.to(DEV), state=state, out=out, act="silu"),
              _batch([b_ - a for _, a, b_ in spans], [slots[r] for r, _, _ in spans]))
         assert float(out[-1].abs().max()) == 0.0
         at = 0
         for r, a, b_ in spans:
             got[r].append(out[at:at + b_ - a].cpu())
             at += b_ - a
-    for r in range(3):
+    for r in range(len(lens)):
         want = silu(causal_conv(xs[r].float(), w, b))
         assert float((torch.cat(got[r]) - want).abs().max()) < 1e-5
-    assert torch.isnan(state[1]).all() and torch.isfinite(state[[0, 2, 3]]).all()
+    assert torch.isnan(state[1]).all() and torch.isfinite(state[[0, 2, 3, 4, 5]]).all()
     if K > 1:
         assert torch.equal(state[3][-1].cpu(), xs[0][-1].float())
 
