@@ -687,14 +687,56 @@ __global__ void gated_norm_kernel(LlmeGatedNormArgs a) {
     }
 }
 
+// Groups of more than 128 and up to 1,024 columns: a block of 128 threads per (token, group) keeps its values in registers
+// between the sum of squares and the output, so y and the gate are read once and all loads are on their way together.
+template <typename T>
+__global__ void __launch_bounds__(128) gated_norm_block_kernel(LlmeGatedNormArgs a) {
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int groups = a.cols / a.group;
+    const int t = blockIdx.x / groups, c0 = (blockIdx.x - t * groups) * a.group;
+    const float* y = a.y + (size_t)t * a.ldy + c0;
+    const T* g = (const T*)a.gate + (size_t)t * a.ldg + c0;
+    T* o = (T*)a.out + (size_t)t * a.ldo + c0;
+    float u[8], gate[8], ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = threadIdx.x + 128 * i;
+        u[i] = c < a.group ? y[c] : 0.0f;
+        gate[i] = c < a.group ? to_f32(g[c]) : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        gate[i] = silu32(gate[i]);
+        if (a.gate_first) u[i] *= gate[i];
+        ss += u[i] * u[i];
+    }
+    const float rinv = 1.0f / sqrtf(block_sum(ss, red) / (float)a.group + a.eps);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = threadIdx.x + 128 * i;
+        if (c >= a.group) continue;
+        float v = u[i] * rinv;
+        if (a.weight) v *= a.weight[c0 + c];
+        if (!a.gate_first) v *= gate[i];
+        o[c] = from_f32<T>(v * a.scale);
+    }
+}
+
 LLME_API int llme_gated_norm(const LlmeGatedNormArgs* args, cudaStream_t stream) {
     const LlmeGatedNormArgs& a = *args;
     if (a.tokens <= 0 || a.cols <= 0) return 0;
     if (!a.y || !a.gate || !a.out) LLME_REFUSE("gated_norm: null pointer");
     if (a.group <= 0 || a.cols % a.group) LLME_REFUSE("gated_norm: %d columns are not whole groups of %d", a.cols, a.group);
     if (!(a.eps > 0.0f)) LLME_REFUSE("gated_norm: eps must be positive");
-    const int warps = 4;
     const long long items = (long long)a.tokens * (a.cols / a.group);
+    if (a.group > 128 && a.group <= 1024 && items < (1LL << 31) && (a.dtype == LLME_F32 || a.dtype == LLME_BF16)) {
+        if (a.dtype == LLME_F32) llme_launch(gated_norm_block_kernel<float>, dim3((unsigned)items), dim3(128), 0, stream, a);
+        else llme_launch(gated_norm_block_kernel<__nv_bfloat16>, dim3((unsigned)items), dim3(128), 0, stream, a);
+        LLME_LAUNCH_STATUS();
+    }
+    const int warps = 4;
     const dim3 grid((unsigned)((items + warps - 1) / warps)), block(32 * warps);
     if (a.dtype == LLME_F32) llme_launch(gated_norm_kernel<float>, grid, block, 0, stream, a);
     else if (a.dtype == LLME_BF16) llme_launch(gated_norm_kernel<__nv_bfloat16>, grid, block, 0, stream, a);

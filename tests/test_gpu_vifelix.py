@@ -182,7 +182,7 @@ def _check_recurrence(gated, H, G, n, p, lens, cuts, slots, scratch_floats, tol)
     assert float(state[max(slots) + 1].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("cols,group", [(64, 16), (30, 30), (36, 6), (512, 128)])
+@pytest.mark.parametrize("cols,group", [(64, 16), (30, 30), (36, 6), (512, 128), (1024, 512), (600, 300), (2048, 1024), (1300, 1300)])
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
 def test_gated_group_norm_kernel(dtype, tol, cols, group):
     """The gate before the norm (the norm sees y silu(g)) and behind it (the norm sees y): the two orders differ."""
