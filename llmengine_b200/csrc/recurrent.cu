@@ -236,7 +236,7 @@ __global__ void rotate_kernel(LlmeRotateArgs a) {
         const int total = a.heads[which] * a.dim;
         const size_t in = (size_t)t * a.ldx[which];
         float* o = a.out[which] + (size_t)t * a.ldo[which];
-        for (int e = threadIdx.x; e < total; e += blockDim.x) {
+        for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < total; e += gridDim.y * blockDim.x) {
             const int h = e / a.dim, d = e - h * a.dim;
             float v;
             if (d >= a.rot_dims) v = load_as_f32(a.x[which], a.dtype, in + e);
@@ -263,7 +263,9 @@ LLME_API int llme_rotate(const LlmeRotateArgs* args, cudaStream_t stream) {
         if (a.x[i] && !a.out[i]) LLME_REFUSE("rotate: no place for a result");
     const int widest = max(a.x[0] ? a.heads[0] : 0, a.x[1] ? a.heads[1] : 0) * a.dim;
     const int threads = widest >= 1024 ? 256 : 128;
-    llme_launch(rotate_kernel, dim3(a.tokens), dim3(threads), 0, stream, a);
+    // a step of few tokens spreads a token's columns over several blocks
+    const int most = (widest + threads - 1) / threads, fill = (592 + a.tokens - 1) / a.tokens;
+    llme_launch(rotate_kernel, dim3(a.tokens, most < fill ? most : fill), dim3(threads), 0, stream, a);
     LLME_LAUNCH_STATUS();
 }
 
@@ -687,8 +689,9 @@ __global__ void gated_norm_kernel(LlmeGatedNormArgs a) {
     }
 }
 
-// Groups of more than 128 and up to 1,024 columns: a block of 128 threads per (token, group) keeps its values in registers
-// between the sum of squares and the output, so y and the gate are read once and all loads are on their way together.
+// Groups of more than 128 and up to 1,024 columns: a block per (token, group), a thread for every eight columns (whole warps),
+// keeps its values in registers between the sum of squares and the output, so y and the gate are read once and all loads are on
+// their way together.
 template <typename T>
 __global__ void __launch_bounds__(128) gated_norm_block_kernel(LlmeGatedNormArgs a) {
     __shared__ float red[32];
@@ -702,7 +705,7 @@ __global__ void __launch_bounds__(128) gated_norm_block_kernel(LlmeGatedNormArgs
     float u[8], gate[8], ss = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const int c = threadIdx.x + 128 * i;
+        const int c = threadIdx.x + blockDim.x * i;
         u[i] = c < a.group ? y[c] : 0.0f;
         gate[i] = c < a.group ? to_f32(g[c]) : 0.0f;
     }
@@ -715,7 +718,7 @@ __global__ void __launch_bounds__(128) gated_norm_block_kernel(LlmeGatedNormArgs
     const float rinv = 1.0f / sqrtf(block_sum(ss, red) / (float)a.group + a.eps);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const int c = threadIdx.x + 128 * i;
+        const int c = threadIdx.x + blockDim.x * i;
         if (c >= a.group) continue;
         float v = u[i] * rinv;
         if (a.weight) v *= a.weight[c0 + c];
@@ -732,8 +735,9 @@ LLME_API int llme_gated_norm(const LlmeGatedNormArgs* args, cudaStream_t stream)
     if (!(a.eps > 0.0f)) LLME_REFUSE("gated_norm: eps must be positive");
     const long long items = (long long)a.tokens * (a.cols / a.group);
     if (a.group > 128 && a.group <= 1024 && items < (1LL << 31) && (a.dtype == LLME_F32 || a.dtype == LLME_BF16)) {
-        if (a.dtype == LLME_F32) llme_launch(gated_norm_block_kernel<float>, dim3((unsigned)items), dim3(128), 0, stream, a);
-        else llme_launch(gated_norm_block_kernel<__nv_bfloat16>, dim3((unsigned)items), dim3(128), 0, stream, a);
+        const dim3 block(((a.group + 7) / 8 + 31) / 32 * 32);
+        if (a.dtype == LLME_F32) llme_launch(gated_norm_block_kernel<float>, dim3((unsigned)items), block, 0, stream, a);
+        else llme_launch(gated_norm_block_kernel<__nv_bfloat16>, dim3((unsigned)items), block, 0, stream, a);
         LLME_LAUNCH_STATUS();
     }
     const int warps = 4;
