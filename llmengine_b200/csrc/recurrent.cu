@@ -614,11 +614,15 @@ static void recurrence_tiles(const LlmeRecurrenceArgs& a, dim3 grid, int pass, i
 }
 
 // The chunk a step of `tokens` tokens whose longest request brings `max_len` is cut by, with room for `slots` piece states
-// (requests of several pieces have fewer than 2 tokens / chunk pieces together); 0: every request is walked whole.
-static int recurrence_chunk(int tokens, int max_len, long long slots) {
+// (requests of several pieces have fewer than 2 tokens / chunk pieces together); 0: every request is walked whole.  A piece's
+// first tile and its state are waited for, so pieces are no shorter than it takes to give the GPU's 148 SMs, 3 blocks each,
+// four rounds of blocks (`blocks` of them work on one piece).
+static int recurrence_chunk(int tokens, int max_len, long long slots, long long blocks) {
     if (slots < 4 || max_len <= REC_MIN_CHUNK) return 0;
     long long chunk = (2LL * tokens + slots - 1) / slots;
     if (chunk < REC_MIN_CHUNK) chunk = REC_MIN_CHUNK;
+    const long long pieces = (4 * 3 * 148 + blocks - 1) / blocks, fill = tokens / pieces / 32 * 32;
+    if (chunk < fill) chunk = fill;
     chunk = (chunk + 31) / 32 * 32;
     return chunk >= max_len ? 0 : (int)chunk;
 }
@@ -643,7 +647,7 @@ LLME_API int llme_recurrence(const LlmeRecurrenceArgs* args, cudaStream_t stream
     }
     const long long hpn = (long long)a.heads * a.p * a.n;
     const long long slots = a.scratch ? a.scratch_floats / (hpn + a.heads) : 0;
-    const int chunk = recurrence_chunk(a.tokens, a.max_len, slots);
+    const int chunk = recurrence_chunk(a.tokens, a.max_len, slots, (long long)((a.p + REC_COLUMNS - 1) / REC_COLUMNS) * a.heads);
     // 16-byte copies where every row of q and k starts on such a boundary
     const int vec = ((uintptr_t)a.q % 16 == 0 && (uintptr_t)a.k % 16 == 0 && a.ldq % 4 == 0 && a.ldk % 4 == 0 && a.n % 4 == 0) ? 1 : 0;
     dim3 grid((a.p + REC_COLUMNS - 1) / REC_COLUMNS, a.heads, a.requests);

@@ -132,7 +132,7 @@ def test_recurrence_kernel(gated, H, G, n, p):
     _check_recurrence(gated, H, G, n, p, [37, 1, 12], [30, 0, 11], [1, 3, 0], 0, 2e-5)
 
 
-@pytest.mark.parametrize("H,G,n,p,room", [(2, 1, 8, 16, 64), (3, 3, 6, 5, 7), (2, 2, 128, 64, 20), (1, 1, 40, 9, 4)])
+@pytest.mark.parametrize("H,G,n,p,room", [(2, 1, 8, 16, 64), (3, 3, 6, 5, 7), (2, 2, 128, 64, 20), (1, 1, 40, 9, 4), (1, 1, 200, 9, 30), (2, 1, 300, 12, 8)])
 @pytest.mark.parametrize("gated", [False, True])
 def test_recurrence_in_pieces(gated, H, G, n, p, room):
     """Long portions cut into pieces that run side by side: requests of one piece, of exactly one and two pieces, one token
