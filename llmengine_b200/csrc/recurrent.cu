@@ -2,8 +2,9 @@
 // channel, the rotation of queries and keys into 32-bit, a linear recurrence with a decaying matrix state per head
 // (linear attention with a fixed decay per head; a selective state space whose decay and step come with every token), and
 // the grouped RMS norm with a silu gate that follows such a recurrence.  Everything that enters the recurrence is 32-bit,
-// and so is the state; a request's tokens are taken in their order, so what a token gets does not depend on how its
-// prompt was cut into steps or on what else the step holds.
+// and so is the state.  A request's tokens are taken in their order; only where a long portion is cut into pieces (by the
+// step's size) does the order of the state's sums change, so what a token gets depends on how its prompt was cut into steps
+// and on what else the step holds by 32-bit rounding and no more.
 #include "common.cuh"
 #include "kernel_args.h"
 
