@@ -8,6 +8,7 @@ from dataclasses import dataclass
 from typing import Any, Callable, Dict, Mapping, Optional, Type
 
 from .bepuzen import BepuzenConfig
+from .funevik import FunevikConfig
 from .qwen3 import ConfigError, Qwen3Config
 from .spec import LayerRun, LayerSpec, ModelSpec, PartSpec
 from .torisun import TorisunConfig
@@ -71,6 +72,7 @@ register_architecture(Qwen3Config.ARCHITECTURE, Qwen3Config)
 register_architecture(BepuzenConfig.ARCHITECTURE, BepuzenConfig)
 register_architecture(TorisunConfig.ARCHITECTURE, TorisunConfig)
 register_architecture(VifelixConfig.ARCHITECTURE, VifelixConfig)
+register_architecture(FunevikConfig.ARCHITECTURE, FunevikConfig)
 
 
 @dataclass
@@ -118,6 +120,6 @@ class EngineConfig:
 
 
 __all__ = [
-    "ARCHITECTURES", "Architecture", "BepuzenConfig", "ConfigError", "EngineConfig", "LayerRun", "LayerSpec", "ModelSpec",
+    "ARCHITECTURES", "Architecture", "BepuzenConfig", "ConfigError", "EngineConfig", "FunevikConfig", "LayerRun", "LayerSpec", "ModelSpec",
     "PartSpec", "Qwen3Config", "TorisunConfig", "VifelixConfig", "config_from_dict", "find_architecture", "load_config", "register_architecture",
 ]

@@ -106,32 +106,38 @@ class Plan:
         kernels.  Activations: "xielu" with params (a_pos, a_neg): z > 0: a_pos z^2 + z/2, else a_neg (exp(z) - 1 - z) + z/2."""
         self._add("linear_act", x=x, w=w, mid=mid, out=out, act=act, params=tuple(float(p) for p in params))
 
-    def pointwise(self, kind: str, a: torch.Tensor, b: Optional[torch.Tensor], out: torch.Tensor, scale: float = 1.0) -> None:
-        """Elementwise over the step's rows (row strides free).  "sigmoid_mul": out = a * sigmoid(b) * scale."""
-        self._add("pointwise", what=kind, a=a, b=b, out=out, scale=float(scale))
+    def pointwise(self, kind: str, a: torch.Tensor, b: Optional[torch.Tensor], out: torch.Tensor, scale: float = 1.0,
+                  group: int = 1) -> None:
+        """Elementwise over the step's rows (row strides free).  "sigmoid_mul": out = a * sigmoid(b) * scale; with
+        `group` > 1, b has one value for every `group` neighbouring columns of a (a gate per head)."""
+        self._add("pointwise", what=kind, a=a, b=b, out=out, scale=float(scale), group=int(group))
 
     def batched_linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         """out[t, b, :] = w[b] x[t, b, :] for every batch member b (one small matrix per head): x [T, B, k] and
         out [T, B, n] are views with free row and member strides, w is [B, n, k]."""
         self._add("batched_linear", x=x, w=w, out=out)
 
-    def residual_add(self, x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor] = None) -> None:
-        """x += a (+ b) in 32-bit: contributions that no following norm adds."""
-        self._add("residual_add", x=x, a=a, b=b)
+    def residual_add(self, x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor] = None,
+                     a_scale: Optional[torch.Tensor] = None, b_scale: Optional[torch.Tensor] = None) -> None:
+        """x += a (+ b) in 32-bit: contributions that no following norm adds.  With `a_scale` / `b_scale` (32-bit vectors
+        of the stream's width) each contribution is multiplied by its vector, column by column, before the sum."""
+        self._add("residual_add", x=x, a=a, b=b, a_scale=a_scale, b_scale=b_scale)
         self.note_copy(x, None)
 
     def latent_attention(self, *, q_rot, kv_in, c_gain, eps: float, inv_freq, rot_dims: int, q, out, cache, group: int,
-                         num_heads: int, kv_rank: int, rot_dim: int, scale: float, sink=None, scratch=None) -> None:
+                         num_heads: int, kv_rank: int, rot_dim: int, scale: float, sink=None, scratch=None, window: int = 0,
+                         interleaved: bool = False) -> None:
         """Attention over a cache of latents, one row [c | rotated key part] per token, shared by all heads.
         `kv_in` [T, kv_rank + rot_dim] is the raw down-projection: its first kv_rank values are RMS-normed with
         `c_gain`, the rest rotated by the token's position (`inv_freq`: rot_dims / 2 frequencies; none: no positions),
         and the row is stored.  `q` [T, H, kv_rank + rot_dim] holds each head's query against the latent already;
         its last rot_dim values are filled here from `q_rot` [T, H, rot_dim] (a strided view), rotated.  Then
-        score = (q . row) * scale, causal, softmax (with `sink` [H]: the denominator also holds exp(sink_h)), and
-        out[t, h, :] = sum_j w_j c_j  [T, H, kv_rank]."""
+        score = (q . row) * scale, causal (with `window` W > 0 query i sees key j only if i - j < W), softmax (with `sink`
+        [H]: the denominator also holds exp(sink_h)), and out[t, h, :] = sum_j w_j c_j  [T, H, kv_rank].  `interleaved`:
+        the rotation pairs coordinate 2i with 2i + 1 instead of i with i + rot_dims / 2."""
         self._add("latent_attention", q_rot=q_rot, kv_in=kv_in, c_gain=c_gain, eps=float(eps), inv_freq=inv_freq,
                   rot_dims=int(rot_dims), q=q, out=out, cache=cache, group=group, num_heads=num_heads, kv_rank=kv_rank,
-                  rot_dim=rot_dim, scale=float(scale), sink=sink, scratch=scratch)
+                  rot_dim=rot_dim, scale=float(scale), sink=sink, scratch=scratch, window=int(window), interleaved=bool(interleaved))
 
     def token_side(self, *, x, a, b, table, offset: int, dim: int, w_gate, w_proj, gain, eps: float, xb, g, y) -> None:
         """x += a (+ b); e = table[token][offset : offset + dim]; g = gelu_tanh(w_gate x) * e; y = w_proj g;
@@ -152,7 +158,7 @@ class Plan:
     def window_attention(self, *, q_in, k_in, v_in, q_gain, k_gain, eps: float, inv_freq, rot_dims: int, amplitude: float,
                          q, out, cache, group: int, num_heads: int, num_kv_heads: int, qk_dim: int, v_dim: int,
                          window: int, keep_first: int, scale: float, sink=None, scratch=None, q_bias=None, k_bias=None,
-                         v_bias=None, head_norm: bool = False) -> None:
+                         v_bias=None, head_norm: bool = False, softcap: float = 0.0, interleaved: bool = False) -> None:
         """Grouped-query attention over a cache whose keys are `qk_dim` and whose values are `v_dim` wide, from the raw
         projections: q_in [T, H qk_dim] and, for a layer that stores, k_in [T, G qk_dim] and v_in [T, G v_dim] (column
         ranges of one product).  With gains, queries and keys are RMS-normed over the WHOLE projection (all heads at
@@ -164,20 +170,27 @@ class Plan:
         parts of single tokens meet whose keys a kernel cuts into ranges.  Options: `q_bias`, `k_bias`, `v_bias` (32-bit
         vectors) are added to the projections first; with `head_norm` every head is normed by itself over its qk_dim
         coordinates and the gains are [qk_dim], shared by the heads; `v_in` may be `k_in` itself (the values are then the
-        keys as projected, before norm and rotation)."""
+        keys as projected, before norm and rotation); `softcap` c > 0: s_ij <- c tanh(s_ij / c) behind the scale;
+        `interleaved`: the rotation pairs coordinate 2i with 2i + 1 instead of i with i + rot_dims / 2.  The projections may
+        be 32-bit where everything else has the type of the products (they then come from a convolution, not a product)."""
         self._add("window_attention", q_bias=q_bias, k_bias=k_bias, v_bias=v_bias, head_norm=bool(head_norm), q_in=q_in, k_in=k_in, v_in=v_in, q_gain=q_gain, k_gain=k_gain, eps=float(eps),
                   inv_freq=inv_freq, rot_dims=int(rot_dims), amplitude=float(amplitude), q=q, out=out, cache=cache, group=group,
                   num_heads=num_heads, num_kv_heads=num_kv_heads, qk_dim=qk_dim, v_dim=v_dim, window=int(window),
-                  keep_first=int(keep_first), scale=float(scale), sink=sink, scratch=scratch)
+                  keep_first=int(keep_first), scale=float(scale), sink=sink, scratch=scratch, softcap=float(softcap),
+                  interleaved=bool(interleaved))
 
-    def moe_route(self, *, logits, top_k: int, scale: float, experts, weights, offsets, order, counts) -> None:
-        """Routing of every token of the step from its router `logits` [T, E] (32-bit): s = sigmoid(logits); C = the
-        `top_k` experts of largest s (`experts` [T, top_k] int32, best first); `weights` [T, top_k]: w_e = scale * s_e /
-        (sum over C of s + 1e-20).  The (token, choice) pairs are then listed expert by expert:
+    def moe_route(self, *, logits, top_k: int, scale: float, experts, weights, offsets, order, counts,
+                  mode: str = "sigmoid") -> None:
+        """Routing of every token of the step from its router `logits` [T, E] (32-bit, any row stride): s = sigmoid(logits);
+        C = the `top_k` experts of largest s (`experts` [T, top_k] int32, best first); `weights` [T, top_k]: w_e = scale *
+        s_e / (sum over C of s + 1e-20).  `mode` "softmax_chosen": C = the experts of largest logits and w_e = scale *
+        exp(z_e) / sum over C of exp(z).  The (token, choice) pairs are then listed expert by expert:
         `offsets` [E + 1] int32 with the pairs of expert e at order[offsets[e] : offsets[e + 1]], a pair being
         token * top_k + choice.  `counts` [E] int32 is scratch that is zero between launches."""
+        if mode not in ("sigmoid", "softmax_chosen"):
+            raise ValueError(f"moe_route: unknown mode {mode!r}")
         self._add("moe_route", logits=logits, top_k=int(top_k), scale=float(scale), experts=experts, weights=weights,
-                  offsets=offsets, order=order, counts=counts)
+                  offsets=offsets, order=order, counts=counts, mode=mode)
 
     def grouped_linear(self, *, x, w, out, offsets, order, top_k: int, gather: bool, scatter: bool, mid=None,
                        act: Optional[str] = None) -> None:
@@ -189,10 +202,10 @@ class Plan:
         self._add("grouped_linear", x=x, w=w, out=out, offsets=offsets, order=order, top_k=int(top_k), gather=bool(gather),
                   scatter=bool(scatter), mid=mid, act=act)
 
-    def moe_combine(self, *, y, weights, base, out) -> None:
+    def moe_combine(self, *, y, weights, base, out, base_gate=None) -> None:
         """out[t] = base[t] (if given) + sum_k weights[t, k] * y[t * top_k + k], the choices added in their order,
-        in 32-bit."""
-        self._add("moe_combine", y=y, weights=weights, base=base, out=out)
+        in 32-bit.  With `base_gate` [T, 1] (32-bit, any row stride) base[t] is first multiplied by sigmoid(base_gate[t])."""
+        self._add("moe_combine", y=y, weights=weights, base=base, out=out, base_gate=base_gate)
 
     def short_conv(self, *, x, w, bias, state, out, act: Optional[str] = "silu") -> None:
         """Causal convolution per channel over each request's tokens: y_t = bias + sum_j w[:, K-1-j] x_(t-j) with zeros
@@ -207,17 +220,39 @@ class Plan:
                   inv_freq=inv_freq)
 
     def recurrence(self, *, q, k, v, state, out, heads: int, n: int, p: int, qk_groups: int, decay=None, dt=None, dt_bias=None,
-                   a_log=None, skip=None, scratch=None) -> None:
+                   a_log=None, skip=None, scratch=None, keep=None, take=None, unit_column: bool = False) -> None:
         """Per request and head, over the request's tokens in order: S_t = a_t S_(t-1) + s_t k_t v_t^T (S is n x p),
         y_t = S_t^T q_t + skip_h v_t.  With `decay` [H]: a_t = decay_h, s_t = 1.  With `dt` [T, H], `dt_bias` and `a_log`
         [H]: d = softplus(dt + dt_bias), a_t = exp(-exp(a_log_h) d), s_t = d.  q, k [T, qk_groups * n] and out [T, H p] are
         32-bit; head h reads group h // (H / qk_groups).  `state` [slots, H, p, n] 32-bit goes from step to step.  With `scratch`
-        (32-bit, a few states large) a long portion is cut into pieces that run side by side."""
+        (32-bit, a few states large) a long portion is cut into pieces that run side by side.  With `keep` and `take` [T, H]
+        (32-bit): a_t = keep[t, h], s_t = take[t, h], both made by an earlier record.  `unit_column`: the last of the p columns
+        has no v behind it, its v_t is one (that column of S sums s_t k_t alone, and that column of y is its product with q);
+        v is then [T, H (p - 1)]."""
         self._add("recurrence", q=q, k=k, v=v, state=state, out=out, heads=int(heads), n=int(n), p=int(p), qk_groups=int(qk_groups),
-                  decay=decay, dt=dt, dt_bias=dt_bias, a_log=a_log, skip=skip, scratch=scratch)
+                  decay=decay, dt=dt, dt_bias=dt_bias, a_log=a_log, skip=skip, scratch=scratch, keep=keep, take=take,
+                  unit_column=bool(unit_column))
 
-    def gated_norm(self, *, y, gate, weight, out, group: int, gate_first: bool, eps: float, scale: float = 1.0) -> None:
-        """RMS norm of y [T, C] (32-bit) in groups of `group` columns, with g = silu(gate): `gate_first`: u = y g,
-        out = u / rms(u) * weight; else out = y / rms(y) * weight * g; then times `scale`.  `weight` [C] 32-bit or None."""
+    def gated_norm(self, *, y, gate, weight, out, group: int, gate_first: bool, eps: float, scale: float = 1.0,
+                   gate_act: str = "silu", floor=None, den_eps: float = 0.0) -> None:
+        """RMS norm of y [T, C] (32-bit) in groups of `group` columns, with g = silu(gate) (`gate_act` "sigmoid": sigmoid(gate)):
+        `gate_first`: u = y g, out = u / rms(u) * weight; else out = y / rms(y) * weight * g; then times `scale`.  `weight` [C]
+        32-bit or None.  With `floor` [T, C / group] (32-bit) every group of y is one column wider than its group of the gate
+        and of out: the extra value d stands behind the group's own, and the group is divided by max(|d|, floor) + den_eps
+        before anything else."""
+        if gate_act not in ("silu", "sigmoid"):
+            raise ValueError(f"gated_norm: unknown gate {gate_act!r}")
         self._add("gated_norm", y=y, gate=gate, weight=weight, out=out, group=int(group), gate_first=bool(gate_first),
-                  eps=float(eps), scale=float(scale))
+                  eps=float(eps), scale=float(scale), gate_act=gate_act, floor=floor, den_eps=float(den_eps))
+
+    def row_norm(self, *, x, gain, eps: float, out) -> None:
+        """out = x / sqrt(mean(x^2) + eps) * gain over the rows of x [T, C]: a norm on (a column range of) a product, in
+        and out of any type and row stride; the arithmetic is 32-bit."""
+        self._add("row_norm", x=x, gain=gain, eps=float(eps), out=out)
+
+    def exp_gates(self, *, i_pre, f_pre, cap: float, state, keep, take, floor) -> None:
+        """The gates of a matrix memory with exponential gating, per request and head over the request's tokens in order,
+        all 32-bit.  From the pre-activations i_pre, f_pre [T, H]: a_t = cap tanh(i_pre / cap), b_t = logsigmoid(cap
+        tanh(f_pre / cap)) (cap 0: no cap); the running maximum M_t = max(b_t + M_(t-1), a_t), kept in `state` [slots, H]
+        (zero when a request starts); keep[t] = exp(b_t + M_(t-1) - M_t), take[t] = exp(a_t - M_t), floor[t] = exp(-M_t)."""
+        self._add("exp_gates", i_pre=i_pre, f_pre=f_pre, cap=float(cap), state=state, keep=keep, take=take, floor=floor)

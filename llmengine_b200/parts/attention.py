@@ -11,7 +11,8 @@ from ..config.spec import PartSpec
 from ..engine.plan import Plan
 from dataclasses import dataclass
 
-from .base import PagedKVSpec, Part, Runtime, WeightSpec, build_part, register_part, run_alone
+from .base import (PagedAndStateSpec, PagedAndStateView, PagedKVSpec, Part, Runtime, StatesSpec, WeightSpec, build_part,
+                   register_part, run_alone)
 
 
 @register_part("mixer", "gqa_attention")
@@ -164,9 +165,16 @@ class WindowSinkAttention(Part):
     * `values_are_keys`: there is no value projection; a token's values are its keys as projected (with the bias,
       before norm and rotation), so v_dim = qk_dim;
     * `gate` "sigmoid": the concatenated heads are multiplied by sigmoid(W_g h) (tensor g) before the output product;
-      W_g reads the same input as the other projections and is stored with them as one matrix.
+      W_g reads the same input as the other projections and is stored with them as one matrix; "sigmoid_head": W_g has one
+      row per head, and head a's output is multiplied by the one number sigmoid((W_g h)_a);
+    * `conv_taps` K > 0: q, k and v each pass a short causal convolution per channel right behind the projection
+      (tensors q.conv, k.conv, v.conv [channels, K], no bias, no activation: y_t = sum_j w[:, j] u_(t - K + 1 + j), zeros
+      before the request's start); the request's last K - 1 projected values are a state beside the pages;
+    * `softcap` c > 0: a score s becomes c tanh(s / c) behind the scale;
+    * `unit_sink`: the softmax's denominator holds one more term of one (a sink whose logit is zero);
+    * a position part with `interleaved` pairs coordinate 2i with 2i + 1.
 
-    Tensors: q, k, v, o; q.norm, k.norm; sink; g; q.b, k.b, v.b.
+    Tensors: q, k, v, o; q.norm, k.norm; sink; g; q.b, k.b, v.b; q.conv, k.conv, v.conv.
 
     Beside `emit` the part has the pieces a mixer of several branches puts together itself: `w_in` (all projections of the
     input as one matrix), `emit_heads` (from that product to the gated heads, times a constant, into a place of the
@@ -176,8 +184,14 @@ class WindowSinkAttention(Part):
                  v_dim: int, scale: float, norm_eps: Optional[float] = None, position_encoding: Optional[PartSpec] = None,
                  window: int = 0, keep_first: int = 0, sink: bool = False, own_kv: bool = True,
                  retain_window: Optional[int] = None, retain_first: Optional[int] = None, head_norm: bool = False,
-                 biases: bool = False, values_are_keys: bool = False, gate: Optional[str] = None):
+                 biases: bool = False, values_are_keys: bool = False, gate: Optional[str] = None, conv_taps: int = 0,
+                 softcap: float = 0.0, unit_sink: bool = False):
         super().__init__(rt, prefix)
+        self.taps, self.softcap, self.unit_sink = int(conv_taps), float(softcap), bool(unit_sink)
+        if self.unit_sink and sink:
+            raise ValueError(f"{prefix}: a learned sink and a sink of one exclude each other")
+        if self.taps and (not own_kv or values_are_keys or biases or norm_eps is not None):
+            raise ValueError(f"{prefix}: the convolution stands behind plain q, k and v projections of the layer's own")
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
         self.hidden, self.nh, self.nkv = int(hidden_size), int(num_heads), int(num_kv_heads)
@@ -190,8 +204,8 @@ class WindowSinkAttention(Part):
             raise ValueError(f"{prefix}: the cache keeps less than the layer's mask needs")
         self.has_sink, self.own_kv = bool(sink), bool(own_kv)
         self.head_norm, self.biases, self.values_are_keys = bool(head_norm), bool(biases), bool(values_are_keys)
-        if gate not in (None, "sigmoid"):
-            raise ValueError(f"{prefix}: unknown output gate {gate!r}; known: sigmoid")
+        if gate not in (None, "sigmoid", "sigmoid_head"):
+            raise ValueError(f"{prefix}: unknown output gate {gate!r}; known: sigmoid, sigmoid_head")
         self.gate = gate
         if self.values_are_keys and self.dv != self.dk:
             raise ValueError(f"{prefix}: values that are the keys have the keys' size, not {self.dv} against {self.dk}")
@@ -205,7 +219,9 @@ class WindowSinkAttention(Part):
         self.heads_size = self.o_size
         self.has_v = self.own_kv and not self.values_are_keys
         self.w_in = self.w_o = self.q_gain = self.k_gain = self.sink = None
-        self.q_bias = self.k_bias = self.v_bias = None
+        self.q_bias = self.k_bias = self.v_bias = self.conv_w = None
+        self.gate_size = 0 if gate is None else (self.nh if gate == "sigmoid_head" else self.o_size)
+        self.conv_channels = self.q_size + self.k_size + self.v_size
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         s = {self.name("q"): WeightSpec((self.q_size, self.hidden)), self.name("o"): WeightSpec((self.hidden, self.o_size))}
@@ -214,7 +230,10 @@ class WindowSinkAttention(Part):
         if self.has_v:
             s[self.name("v")] = WeightSpec((self.v_size, self.hidden))
         if self.gate is not None:
-            s[self.name("g")] = WeightSpec((self.o_size, self.hidden))
+            s[self.name("g")] = WeightSpec((self.gate_size, self.hidden))
+        if self.taps:
+            for n, c in (("q", self.q_size), ("k", self.k_size), ("v", self.v_size)):
+                s[self.name(n + ".conv")] = WeightSpec((c, self.taps), role="vector", init="unit")
         if self.eps is not None:
             s[self.name("q.norm")] = WeightSpec((self.dk if self.head_norm else self.q_size,), role="vector", init="gain")
             if self.own_kv:
@@ -239,6 +258,10 @@ class WindowSinkAttention(Part):
             self.q_gain = t[self.name("q.norm")].float().contiguous()
             self.k_gain = t[self.name("k.norm")].float().contiguous() if self.own_kv else None
         self.sink = t[self.name("sink")].float().contiguous() if self.has_sink else None
+        if self.unit_sink:
+            self.sink = torch.zeros(self.nh, dtype=torch.float32, device=self.w_in.device)
+        if self.taps:
+            self.conv_w = torch.cat([t[self.name(n + ".conv")].float() for n in ("q", "k", "v")], 0).contiguous()
         if self.biases:
             self.q_bias = t[self.name("q.b")].float().contiguous()
             self.k_bias = t[self.name("k.b")].float().contiguous() if self.own_kv else None
@@ -247,39 +270,55 @@ class WindowSinkAttention(Part):
     @property
     def in_size(self) -> int:
         """Rows of `w_in`: the width of the product that holds every projection of the mixer's input."""
-        return self.q_size + (self.k_size if self.own_kv else 0) + (self.v_size if self.has_v else 0) + (self.o_size if self.gate else 0)
+        return self.q_size + (self.k_size if self.own_kv else 0) + (self.v_size if self.has_v else 0) + self.gate_size
 
-    def cache_spec(self) -> SplitKVSpec:
-        return SplitKVSpec(self.nkv, self.dk, self.dv, self.retain_window, self.retain_first)
+    def cache_spec(self):
+        pages = SplitKVSpec(self.nkv, self.dk, self.dv, self.retain_window, self.retain_first)
+        if not self.taps:
+            return pages
+        return PagedAndStateSpec(pages, StatesSpec((("conv", (max(self.taps - 1, 1), self.conv_channels)),)))
 
     def emit_heads(self, plan: Plan, proj: torch.Tensor, cache, out: torch.Tensor, scale: float = 1.0) -> None:
         """From `proj` = h w_in^T [T, in_size] to the heads [T, num_heads v_dim] (gated, where the layer has a gate), times
         `scale`, written to `out` (any row stride)."""
         rt = self.rt
+        states = None
+        if isinstance(cache, PagedAndStateView):
+            cache, states = cache.paged, cache.state
         if cache.writes != self.own_kv:
             raise ValueError(f"{self.prefix}: a layer with key and value projections keeps a cache of its own, one "
                              f"without reads another layer's")
         qs, ks = self.q_size, self.k_size
         q = rt.workspace("q", qs, rt.dtype)
-        k_in = proj[:, qs:qs + ks] if self.own_kv else None
-        v_in = (k_in if self.values_are_keys else proj[:, qs + ks:qs + ks + self.v_size]) if self.own_kv else None
+        src = proj
+        if self.taps:
+            # the convolution's results stay 32-bit up to the rotation; the finished queries and the cached keys and
+            # values then take the type of the products
+            if states is None:
+                raise ValueError(f"{self.prefix}: the convolution needs its state beside the pages")
+            src = rt.workspace("qkv_conv", self.conv_channels, torch.float32)
+            plan.short_conv(x=proj[:, :self.conv_channels], w=self.conv_w, bias=None, state=states.states["conv"], out=src, act=None)
+        k_in = src[:, qs:qs + ks] if self.own_kv else None
+        v_in = (k_in if self.values_are_keys else src[:, qs + ks:qs + ks + self.v_size]) if self.own_kv else None
         gated = self.gate is not None
         heads = rt.workspace("attn_out", self.o_size, rt.dtype) if (gated or scale != 1.0 or not out.is_contiguous()) else out
         pos = self.position
         plan.window_attention(
-            q_in=proj[:, :qs], k_in=k_in, v_in=v_in,
+            q_in=src[:, :qs], k_in=k_in, v_in=v_in,
             q_gain=self.q_gain, k_gain=self.k_gain, eps=self.eps or 0.0,
             inv_freq=pos.frequencies() if pos is not None else None, rot_dims=pos.dims if pos is not None else 0,
             amplitude=pos.amplitude if pos is not None else 1.0, q=q, out=heads, cache=cache.kv, group=cache.group,
             num_heads=self.nh, num_kv_heads=self.nkv, qk_dim=self.dk, v_dim=self.dv, window=self.window,
             keep_first=self.keep_first, scale=self.scale, sink=self.sink,
-            q_bias=self.q_bias, k_bias=self.k_bias, v_bias=self.v_bias, head_norm=self.head_norm,
+            q_bias=self.q_bias, k_bias=self.k_bias, v_bias=self.v_bias, head_norm=self.head_norm, softcap=self.softcap,
+            interleaved=bool(pos is not None and getattr(pos, "interleaved", False)),
             # up to 8 key ranges per decoded token: a maximum, a sum and an output row per range and head
             scratch=(rt.buffer("window_attention_scratch", 1, rt.max_requests * self.nh * 8 * (self.dv + 2), torch.float32,
                                exact=True).view(-1) if rt.dtype == torch.bfloat16 else None))
         if gated:
-            g0 = self.in_size - self.o_size
-            plan.pointwise("sigmoid_mul", heads, proj[:, g0:g0 + self.o_size], out, scale=scale)
+            g0 = self.in_size - self.gate_size
+            plan.pointwise("sigmoid_mul", heads, proj[:, g0:g0 + self.gate_size], out, scale=scale,
+                           group=self.dv if self.gate == "sigmoid_head" else 1)
         elif heads is not out:
             raise ValueError(f"{self.prefix}: heads without a gate go to a dense place of their own, unscaled")
 

@@ -70,11 +70,19 @@ class ParallelResidualBlock(Part):
     have no feed-forward.  With a "token_side" part, that part follows on the updated x (and does the addition of
     the sublayers' contributions itself, in the same pass).
 
-    The block reads the parts "norm", "mixer" and, where the layer has them, "feed_forward" and "token_side".
+    Options of other designs: with a part "feed_forward_norm" the feed-forward reads a norm of its own of the same x
+    (x = x + mixer(norm(x)) + feed_forward(feed_forward_norm(x))); with `mixer_scale_name` / `feed_forward_scale_name`
+    each sublayer's result is multiplied, column by column, by a learned vector of the stream's width (tensors of those
+    names below the layer's prefix) before the sum.
+
+    The block reads the parts "norm", "mixer" and, where the layer has them, "feed_forward", "feed_forward_norm" and
+    "token_side".
     """
 
     def __init__(self, rt: Runtime, prefix: str, layer: LayerSpec, norm_name: str = "norm", mixer_name: str = "mixer",
-                 feed_forward_name: str = "feed_forward", token_side_name: str = "token_side"):
+                 feed_forward_name: str = "feed_forward", token_side_name: str = "token_side",
+                 feed_forward_norm_name: str = "feed_forward_norm", mixer_scale_name: Optional[str] = None,
+                 feed_forward_scale_name: Optional[str] = None, hidden_size: Optional[int] = None):
         super().__init__(rt, prefix)
         missing = [n for n in ("norm", "mixer") if n not in layer.parts]
         if missing:
@@ -83,20 +91,31 @@ class ParallelResidualBlock(Part):
         self.mixer = build_part("mixer", layer.parts["mixer"], rt, self.name(mixer_name))
         self.ffn = (build_part("feed_forward", layer.parts["feed_forward"], rt, self.name(feed_forward_name))
                     if "feed_forward" in layer.parts else None)
+        self.ffn_norm = (build_part("norm", layer.parts["feed_forward_norm"], rt, self.name(feed_forward_norm_name))
+                         if self.ffn is not None and "feed_forward_norm" in layer.parts else None)
         self.side = (build_part("token_side", layer.parts["token_side"], rt, self.name(token_side_name))
                      if "token_side" in layer.parts else None)
-        self.parts = tuple(p for p in (self.norm, self.mixer, self.ffn, self.side) if p is not None)
+        self.scale_names = (mixer_scale_name, feed_forward_scale_name if self.ffn is not None else None)
+        if any(self.scale_names) and (hidden_size is None or self.side is not None):
+            raise ValueError(f"layer {prefix!r}: scale vectors need the stream's width and a block without a token side input")
+        self.hidden = None if hidden_size is None else int(hidden_size)
+        self.scales = [None, None]
+        self.parts = tuple(p for p in (self.norm, self.mixer, self.ffn_norm, self.ffn, self.side) if p is not None)
         self.capture_safe = all(p.capture_safe and hasattr(p, "emit") for p in self.parts)
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         out: Dict[str, WeightSpec] = {}
         for p in self.parts:
             out.update(p.weight_specs())
+        for n in self.scale_names:
+            if n:
+                out[self.name(n)] = WeightSpec((self.hidden,), role="vector", init="gain")
         return out
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
         for p in self.parts:
             p.load_weights({n: tensors[n] for n in p.weight_specs()})
+        self.scales = [tensors[self.name(n)].float().contiguous() if n else None for n in self.scale_names]
 
     def tied_tensors(self) -> Dict[str, str]:
         out: Dict[str, str] = {}
@@ -117,13 +136,22 @@ class ParallelResidualBlock(Part):
         hidden = x.shape[1]
         h = emit_norm(plan, self.norm, x, delta=delta)
         a = emit_mixer(plan, self.mixer, h, cache, hidden)
-        b = emit_feed_forward(plan, self.ffn, h, hidden) if self.ffn is not None else None
+        b = None
+        if self.ffn is not None:
+            # a second norm of the same x goes to a workspace of its own: the mixer's input may still be needed
+            if self.ffn_norm is None:
+                h2 = h
+            elif hasattr(self.ffn_norm, "emit"):
+                h2 = self.ffn_norm.emit(plan, x, out_name="normed_second")
+            else:
+                h2 = emit_norm(plan, self.ffn_norm, x)
+            b = emit_feed_forward(plan, self.ffn, h2, hidden)
         if self.side is not None:
             self.side.emit(plan, x, a, b)
             return x, None
-        if b is None:
+        if b is None and self.scales[0] is None:
             return x, a                       # the next norm adds it
-        plan.residual_add(x, a, b)
+        plan.residual_add(x, a, b, a_scale=self.scales[0], b_scale=self.scales[1] if b is not None else None)
         return x, None
 
     def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], batch, cache):

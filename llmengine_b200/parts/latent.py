@@ -58,15 +58,19 @@ class PartialRotaryEncoding(Part):
     makes t turns over the original length, lo = max(floor(turns(fast)), 0), hi = min(ceil(turns(slow)), dims - 1) and
     r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency becomes f_i / factor * r_i + f_i (1 - r_i) (fast
     coordinates keep their frequency, slow ones are slowed), and cosine and sine are multiplied by
-    `amplitude` = 0.1 ln(factor) + 1."""
+    `amplitude` = 0.1 ln(factor) + 1.
+
+    `interleaved`: coordinate 2i pairs with 2i + 1 instead (same frequencies, same turn): (u, v) -> (u cos - v sin,
+    v cos + u sin)."""
 
     needs_apply = True
 
-    def __init__(self, rt: Runtime, prefix: str, dims: int, base: float, scaling: Optional[dict] = None):
+    def __init__(self, rt: Runtime, prefix: str, dims: int, base: float, scaling: Optional[dict] = None,
+                 interleaved: bool = False):
         super().__init__(rt, prefix)
         if dims <= 0 or dims % 2:
             raise ValueError(f"rotary encoding needs an even number of rotated coordinates, got {dims}")
-        self.dims, self.base = int(dims), float(base)
+        self.dims, self.base, self.interleaved = int(dims), float(base), bool(interleaved)
         self.scaling = None if not scaling else tuple(float(scaling[k]) for k in ("factor", "original", "fast", "slow"))
         self.amplitude = 1.0 if self.scaling is None else float(np.float32(0.1 * np.log(self.scaling[0]) + 1.0))
 
@@ -101,18 +105,22 @@ class LatentAttention(Part):
     key = [W_uk c | rotated part], value = W_uv c; score = q . key * scale, causal; softmax, with `sink` a learned
     number per head whose exponential joins the denominator; with `output_gate` the concatenated heads are
     multiplied by sigmoid(W_g h); then W_o.  `rot_dim` = 0 with no position encoding: no rotated part at all.
+    With `q_rank` > 0 the queries come through a latent of their own: c_q = rmsnorm(W_dq h) with a weight vector
+    (dq.norm), q = W_uq c_q (tensors dq, dq.norm, uq instead of q).  With `window` W > 0 a query sees only the last W
+    keys, its own included, and the cache gives pages back as the window passes them.
 
-    Stored as: one matrix [W_q | W_dkv | W_g] (one product serves the three), W_uk transposed per head
+    Stored as: one matrix [W_q or W_dq | W_dkv | W_g] (one product serves the three), W_uk transposed per head
     [H, kv_rank, nope_dim] (it carries queries into the latent space), W_uv per head [H, v_dim, kv_rank].
     """
 
     def __init__(self, rt: Runtime, prefix: str, hidden_size: int, num_heads: int, nope_dim: int, rot_dim: int,
                  v_dim: int, kv_rank: int, scale: float, norm_eps: float, position_encoding: Optional[PartSpec] = None,
-                 sink: bool = False, output_gate: bool = False):
+                 sink: bool = False, output_gate: bool = False, q_rank: int = 0, window: int = 0):
         super().__init__(rt, prefix)
         self.hidden, self.nh, self.dn, self.dr = int(hidden_size), int(num_heads), int(nope_dim), int(rot_dim)
         self.dv, self.rank, self.scale, self.eps = int(v_dim), int(kv_rank), float(scale), float(norm_eps)
         self.has_sink, self.has_gate = bool(sink), bool(output_gate)
+        self.q_rank, self.window = int(q_rank), int(window)
         if (self.dr > 0) != (position_encoding is not None):
             raise ValueError(f"{prefix}: a rotated part needs a position encoding, and a position encoding a rotated part")
         self.position = build_part("position", position_encoding, rt, prefix) if position_encoding is not None else None
@@ -121,18 +129,23 @@ class LatentAttention(Part):
         self.q_size = self.nh * (self.dn + self.dr)
         self.kv_size = self.rank + self.dr
         self.o_size = self.nh * self.dv
-        self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.c_gain = self.sink = None
+        self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.c_gain = self.sink = self.w_uq = self.q_gain = None
 
     # ------------------------------------------------------------------ weights
     def weight_specs(self) -> Dict[str, WeightSpec]:
         s = {
-            self.name("q"): WeightSpec((self.q_size, self.hidden)),
             self.name("dkv"): WeightSpec((self.kv_size, self.hidden)),
             self.name("dkv.norm"): WeightSpec((self.rank,), role="vector", init="gain"),
             self.name("uk"): WeightSpec((self.nh * self.dn, self.rank)),
             self.name("uv"): WeightSpec((self.o_size, self.rank)),
             self.name("o"): WeightSpec((self.hidden, self.o_size)),
         }
+        if self.q_rank:
+            s[self.name("dq")] = WeightSpec((self.q_rank, self.hidden))
+            s[self.name("dq.norm")] = WeightSpec((self.q_rank,), role="vector", init="gain")
+            s[self.name("uq")] = WeightSpec((self.q_size, self.q_rank))
+        else:
+            s[self.name("q")] = WeightSpec((self.q_size, self.hidden))
         if self.has_sink:
             s[self.name("sink")] = WeightSpec((self.nh,), role="vector", init="unit")
         if self.has_gate:
@@ -140,8 +153,11 @@ class LatentAttention(Part):
         return s
 
     def load_weights(self, t: Dict[str, torch.Tensor]) -> None:
-        parts = [t[self.name("q")], t[self.name("dkv")]] + ([t[self.name("g")]] if self.has_gate else [])
+        parts = [t[self.name("dq" if self.q_rank else "q")], t[self.name("dkv")]] + ([t[self.name("g")]] if self.has_gate else [])
         self.w_in = torch.cat(parts, dim=0).contiguous()
+        if self.q_rank:
+            self.w_uq = t[self.name("uq")].contiguous()
+            self.q_gain = t[self.name("dq.norm")].contiguous()
         self.w_uk_t = t[self.name("uk")].view(self.nh, self.dn, self.rank).transpose(1, 2).contiguous()
         self.w_uv = t[self.name("uv")].view(self.nh, self.dv, self.rank).contiguous()
         self.w_o = t[self.name("o")].contiguous()
@@ -149,7 +165,7 @@ class LatentAttention(Part):
         self.sink = t[self.name("sink")].float().contiguous() if self.has_sink else None
 
     def cache_spec(self) -> LatentKVSpec:
-        return LatentKVSpec(self.kv_size)
+        return LatentKVSpec(self.kv_size, self.window)
 
     # ------------------------------------------------------------------ compute
     def emit(self, plan: Plan, h: torch.Tensor, cache) -> torch.Tensor:
@@ -161,8 +177,16 @@ class LatentAttention(Part):
         width = self.w_in.shape[0]
         proj = rt.workspace("latent_in", width, rt.dtype)
         plan.linear(h, self.w_in, proj)
-        q_heads = proj[:, :self.q_size].view(T, H, dn + dr)
-        kv_in = proj[:, self.q_size:self.q_size + self.kv_size]
+        first = self.q_rank or self.q_size                       # columns of the product that belong to the queries
+        if self.q_rank:
+            cq = rt.workspace("latent_cq", self.q_rank, rt.dtype)
+            plan.row_norm(x=proj[:, :first], gain=self.q_gain, eps=self.eps, out=cq)
+            q_full = rt.workspace("latent_q_heads", self.q_size, rt.dtype)
+            plan.linear(cq, self.w_uq, q_full)
+            q_heads = q_full.view(T, H, dn + dr)
+        else:
+            q_heads = proj[:, :first].view(T, H, dn + dr)
+        kv_in = proj[:, first:first + self.kv_size]
         q = rt.workspace("latent_q", H * (r + dr), rt.dtype)
         q3 = q.view(T, H, r + dr)
         plan.batched_linear(q_heads[:, :, :dn], self.w_uk_t, q3[:, :, :r])
@@ -171,11 +195,12 @@ class LatentAttention(Part):
                               inv_freq=self.position.frequencies() if self.position is not None else None,
                               rot_dims=self.position.dims if self.position is not None else 0, q=q, out=out,
                               cache=cache.kv, group=cache.group, num_heads=H, kv_rank=r, rot_dim=dr, scale=self.scale,
-                              sink=self.sink, scratch=rt.latent_scratch(H, r))
+                              sink=self.sink, scratch=rt.latent_scratch(H, r), window=self.window,
+                              interleaved=bool(self.position is not None and self.position.interleaved))
         heads = rt.workspace("latent_heads", self.o_size, rt.dtype)
         plan.batched_linear(out.view(T, H, r), self.w_uv, heads.view(T, H, dv))
         if self.has_gate:
-            plan.pointwise("sigmoid_mul", heads, proj[:, self.q_size + self.kv_size:], heads)
+            plan.pointwise("sigmoid_mul", heads, proj[:, first + self.kv_size:], heads)
         delta = rt.workspace("mixer_out", self.hidden, torch.float32)
         plan.linear(heads, self.w_o, delta)
         return delta

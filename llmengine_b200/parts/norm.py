@@ -29,8 +29,9 @@ class RMSNorm(Part):
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.gain = tensors[self.name(self.leaf)]
 
-    def emit(self, plan: Plan, x: torch.Tensor, delta: Optional[torch.Tensor] = None, rows: str = ROWS_TOKENS) -> torch.Tensor:
-        out = self.rt.workspace("normed" if rows == ROWS_TOKENS else "normed_rows", self.size, self.rt.dtype)
+    def emit(self, plan: Plan, x: torch.Tensor, delta: Optional[torch.Tensor] = None, rows: str = ROWS_TOKENS,
+             out_name: Optional[str] = None) -> torch.Tensor:
+        out = self.rt.workspace(out_name or ("normed" if rows == ROWS_TOKENS else "normed_rows"), self.size, self.rt.dtype)
         plan.rmsnorm(x, self.gain, self.eps, out, delta=delta, rows=rows)
         return out
 

@@ -9,6 +9,13 @@
   q, k, v and a gate come from one product; q and k are rotated by position, k then times qk_dim^(-1/2);
   S_t = decay_a S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t;  every head's o is divided by its root mean square, the heads are
   multiplied by silu(gate) and projected.  State per request: the matrices S (32-bit).
+* `MatrixMemory` (kind `matrix_memory`): a matrix memory with exponential input and forget gates, kept in range by a running
+  maximum of the gates' logarithms.  Per head: q = W_q h / sqrt(d), k = W_k h, v = W_v h; log gates a_t = cap tanh((W_i h +
+  b_i) / cap) and b_t = logsigmoid(cap tanh((W_f h + b_f) / cap)); M_t = max(b_t + M_(t-1), a_t), M_0 = 0;
+  S_t = exp(b_t + M_(t-1) - M_t) S_(t-1) + exp(a_t - M_t) k_t v_t^T and n_t the same with k_t alone;
+  o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-M_t)) + 1e-6); every head's o is divided by its root mean square, the heads are
+  multiplied by a weight vector and by sigmoid(W_g h), and projected.  State per request: S and n (n is one more column of
+  S, whose v is one) and M, all 32-bit.
 * `ParallelMixer` (kind `parallel`): branches that read the same input; the result is sum_b scale_b branch_b(h).  The
   branches' input projections are ONE product, and so are their output projections: every branch writes its gated heads,
   times its scale, into its columns of one row, and the output matrices stand side by side.
@@ -148,6 +155,74 @@ class Retention(Part):
         plan.linear(h, self.w_in, proj)
         heads = rt.workspace("retention_heads", self.heads_size, rt.dtype)
         self.emit_heads(plan, proj, cache, heads)
+        delta = rt.workspace("mixer_out", self.hidden, torch.float32)
+        plan.linear(heads, self.w_o, delta)
+        return delta
+
+    def forward(self, h: torch.Tensor, batch, cache) -> torch.Tensor:
+        plan = Plan()
+        buf = self.rt.workspace("normed", self.hidden, self.rt.dtype)
+        buf[: h.shape[0]].copy_(h)
+        delta = self.emit(plan, buf, cache)
+        run_alone(self.rt, plan, batch)
+        return delta[: h.shape[0]]
+
+
+@register_part("mixer", "matrix_memory")
+class MatrixMemory(Part):
+    """Tensors: q, k [heads qk_dim, hidden]; v, g [heads v_dim, hidden]; i, f [heads, hidden] with biases i.b, f.b; norm
+    [heads v_dim]; o [hidden, heads v_dim].  `gate_cap` 0: the gates' pre-activations are not capped.  q, k, v and g are one
+    product in the type of the products; the gates' pre-activations are a second, small one whose result is 32-bit."""
+
+    DEN_EPS = 1e-6                       # what the design adds to the denominator max(|n . q|, exp(-M))
+
+    def __init__(self, rt: Runtime, prefix: str, hidden_size: int, num_heads: int, qk_dim: int, v_dim: int, gate_cap: float,
+                 norm_eps: float):
+        super().__init__(rt, prefix)
+        self.hidden, self.nh, self.dk, self.dv = int(hidden_size), int(num_heads), int(qk_dim), int(v_dim)
+        self.cap, self.eps = float(gate_cap), float(norm_eps)
+        self.qk_size, self.heads_size = self.nh * self.dk, self.nh * self.dv
+        self.in_size = 2 * self.qk_size + 2 * self.heads_size
+        self.w_in = self.w_gates = self.b_gates = self.w_o = self.norm_w = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        v = lambda n, init="normal": WeightSpec((n,), role="vector", init=init)
+        return {self.name("q"): WeightSpec((self.qk_size, self.hidden)), self.name("k"): WeightSpec((self.qk_size, self.hidden)),
+                self.name("v"): WeightSpec((self.heads_size, self.hidden)), self.name("g"): WeightSpec((self.heads_size, self.hidden)),
+                self.name("o"): WeightSpec((self.hidden, self.heads_size)), self.name("norm"): v(self.heads_size, "gain"),
+                self.name("i"): WeightSpec((self.nh, self.hidden)), self.name("i.b"): v(self.nh, "unit"),
+                self.name("f"): WeightSpec((self.nh, self.hidden)), self.name("f.b"): v(self.nh, "unit")}
+
+    def load_weights(self, t: Dict[str, torch.Tensor]) -> None:
+        self.w_in = torch.cat([t[self.name(n)] for n in ("q", "k", "v", "g")], 0).contiguous()
+        self.w_gates = torch.cat([t[self.name("i")], t[self.name("f")]], 0).contiguous()
+        self.b_gates = torch.cat([t[self.name("i.b")].float(), t[self.name("f.b")].float()]).contiguous()
+        self.w_o = t[self.name("o")].contiguous()
+        self.norm_w = t[self.name("norm")].float().contiguous()
+
+    def cache_spec(self) -> StatesSpec:
+        return StatesSpec((("state", (self.nh, self.dv + 1, self.dk)), ("max", (self.nh,))))
+
+    def emit(self, plan: Plan, h: torch.Tensor, cache: StatesView) -> torch.Tensor:
+        rt, H, qs, hs = self.rt, self.nh, self.qk_size, self.heads_size
+        proj = rt.workspace("memory_in", self.in_size, rt.dtype)
+        plan.linear(h, self.w_in, proj)
+        pre = rt.workspace("memory_gates_in", 2 * H, torch.float32)
+        plan.linear(h, self.w_gates, pre, bias=self.b_gates)
+        gates = rt.workspace("memory_gates", 3 * H, torch.float32)          # [keep | take | floor]
+        plan.exp_gates(i_pre=pre[:, :H], f_pre=pre[:, H:], cap=self.cap, state=cache.states["max"], keep=gates[:, :H],
+                       take=gates[:, H:2 * H], floor=gates[:, 2 * H:])
+        q32 = rt.workspace("memory_q", qs, torch.float32)
+        k32 = rt.workspace("memory_k", qs, torch.float32)
+        plan.rotate(x=(proj[:, :qs], proj[:, qs:2 * qs]), out=(q32, k32), heads=(H, H), scale=(float(self.dk) ** -0.5, 1.0),
+                    dim=self.dk, rot_dims=0, inv_freq=None)
+        o = rt.workspace("memory_o", H * (self.dv + 1), torch.float32)
+        plan.recurrence(q=q32, k=k32, v=proj[:, 2 * qs:2 * qs + hs], state=cache.states["state"], out=o, heads=H, n=self.dk,
+                        p=self.dv + 1, qk_groups=H, keep=gates[:, :H], take=gates[:, H:2 * H], unit_column=True,
+                        scratch=rt.recurrence_scratch(H, self.dv + 1, self.dk))
+        heads = rt.workspace("memory_heads", hs, rt.dtype)
+        plan.gated_norm(y=o, gate=proj[:, 2 * qs + hs:], weight=self.norm_w, out=heads, group=self.dv, gate_first=False,
+                        eps=self.eps, gate_act="sigmoid", floor=gates[:, 2 * H:], den_eps=self.DEN_EPS)
         delta = rt.workspace("mixer_out", self.hidden, torch.float32)
         plan.linear(heads, self.w_o, delta)
         return delta

@@ -116,9 +116,12 @@ class HostOps:
         ap, an = params
         out.copy_(torch.where(z > 0, ap * z * z + 0.5 * z, an * (torch.expm1(torch.clamp(z, max=0)) - z) + 0.5 * z).to(out.dtype))
 
-    def pointwise(self, kind, a, b, out, scale=1.0):
+    def pointwise(self, kind, a, b, out, scale=1.0, group=1):
         assert kind == "sigmoid_mul"
-        out.copy_((a.float() * torch.sigmoid(b.float()) * scale).to(out.dtype))
+        g = torch.sigmoid(b.float())
+        if group > 1:
+            g = g.repeat_interleave(group, 1)
+        out.copy_((a.float() * g * scale).to(out.dtype))
 
     # ---- layers with a state of fixed size per request
     @staticmethod
@@ -162,8 +165,13 @@ class HostOps:
             for t in range(lo, hi):
                 q = a["q"][t].view(G, n).repeat_interleave(rep, 0)
                 k = a["k"][t].view(G, n).repeat_interleave(rep, 0)
-                v = a["v"][t].float().view(H, p)
-                if a["dt"] is None:
+                if a.get("unit_column"):
+                    v = torch.cat([a["v"][t].float().view(H, p - 1), torch.ones(H, 1)], 1)
+                else:
+                    v = a["v"][t].float().view(H, p)
+                if a.get("keep") is not None:
+                    decay, step = a["keep"][t], a["take"][t]
+                elif a["dt"] is None:
                     decay, step = a["decay"], torch.ones(H)
                 else:
                     z = a["dt"][t].float() + (a["dt_bias"] if a["dt_bias"] is not None else 0.0)
@@ -177,7 +185,11 @@ class HostOps:
 
     def gated_norm(self, a, T):
         y, g = a["y"][:T], a["gate"][:T].float()
-        gate = g * torch.sigmoid(g)
+        gate = torch.sigmoid(g) if a.get("gate_act", "silu") == "sigmoid" else g * torch.sigmoid(g)
+        if a.get("floor") is not None:
+            wide = y.reshape(T, -1, a["group"] + 1)
+            den = torch.maximum(wide[..., -1].abs(), a["floor"][:T]) + a["den_eps"]
+            y = (wide[..., :-1] / den[..., None]).reshape(T, -1)
         u = y * gate if a["gate_first"] else y
         parts = u.view(T, -1, a["group"])
         u = (parts / torch.sqrt((parts * parts).mean(-1, keepdim=True) + a["eps"])).reshape(T, -1)
@@ -187,15 +199,37 @@ class HostOps:
             u = u * gate
         a["out"][:T] = (u * a["scale"]).to(a["out"].dtype)
 
+    def row_norm(self, a, T):
+        x = a["x"][:T].float()
+        a["out"][:T] = (x * (1.0 / torch.sqrt((x * x).mean(-1, keepdim=True) + a["eps"])) * a["gain"].float()).to(a["out"].dtype)
+
+    def exp_gates(self, a, batch):
+        cap = a["cap"]
+        for lo, hi, slot in self._requests(batch):
+            M = a["state"][slot]
+            for t in range(lo, hi):
+                i, f = a["i_pre"][t].float(), a["f_pre"][t].float()
+                if cap > 0:
+                    i, f = cap * torch.tanh(i / cap), cap * torch.tanh(f / cap)
+                f = torch.clamp(f, max=0) - torch.log1p(torch.exp(-f.abs()))
+                new = torch.maximum(f + M, i)
+                a["keep"][t] = torch.exp(f + M - new)
+                a["take"][t] = torch.exp(i - new)
+                a["floor"][t] = torch.exp(-new)
+                M.copy_(new)
+
     def batched_linear(self, x, w, out):
         out.copy_(torch.einsum("tbk,bnk->tbn", x.float(), w.float()).to(out.dtype))
 
     @staticmethod
-    def _rotate(x, positions, inv_freq, dims):
+    def _rotate(x, positions, inv_freq, dims, interleaved=False, amplitude=1.0):
         half = dims // 2
         ang = positions.float()[:, None] * inv_freq.float()[None, :]
         shape = [x.shape[0]] + [1] * (x.dim() - 2) + [half]
-        c, s = torch.cos(ang).reshape(shape), torch.sin(ang).reshape(shape)
+        c, s = (torch.cos(ang) * amplitude).reshape(shape), (torch.sin(ang) * amplitude).reshape(shape)
+        if interleaved:
+            u, v = x[..., 0:dims:2], x[..., 1:dims:2]
+            return torch.cat([torch.stack([u * c - v * s, v * c + u * s], -1).flatten(-2), x[..., dims:]], -1)
         u, v = x[..., :half], x[..., half:dims]
         return torch.cat([u * c - v * s, v * c + u * s, x[..., dims:]], -1)
 
@@ -207,8 +241,9 @@ class HostOps:
         c = c * (1.0 / torch.sqrt((c * c).mean(-1, keepdim=True) + a["eps"])) * a["c_gain"].float()
         row = c
         if dr:
-            row = torch.cat([c, self._rotate(kv[:, r:], positions, a["inv_freq"], a["rot_dims"])], -1)
-            q[:, :, r:] = self._rotate(a["q_rot"][:T].float(), positions, a["inv_freq"], a["rot_dims"]).to(q.dtype)
+            il = bool(a.get("interleaved"))
+            row = torch.cat([c, self._rotate(kv[:, r:], positions, a["inv_freq"], a["rot_dims"], il)], -1)
+            q[:, :, r:] = self._rotate(a["q_rot"][:T].float(), positions, a["inv_freq"], a["rot_dims"], il).to(q.dtype)
         flat = cache.view(-1, r + dr)
         for t in range(T):
             if int(slot_mapping[t]) >= 0:
@@ -216,20 +251,25 @@ class HostOps:
         for t in range(T):
             p = int(positions[t])
             bt = block_tables[int(token_request[t])]
-            js = torch.arange(0, p + 1)
+            W = a.get("window", 0)
+            js = torch.arange(max(0, p - W + 1) if W > 0 else 0, p + 1)
             pages = bt[(js // page_size).long()].long()
             assert (pages >= 0).all(), "attention would read a page that is not held"
             rows = flat[pages * page_size + (js % page_size)].float()            # [n, r + dr]
             s = (q[t].float() @ rows.t()) * a["scale"]                           # [H, n]
             if a["sink"] is not None:
                 s = torch.cat([s, a["sink"].float()[:, None]], -1)
-            w = torch.softmax(s, -1)[:, : p + 1]
+            w = torch.softmax(s, -1)[:, : js.numel()]
             out[t] = (w @ rows[:, :r]).to(out.dtype)
 
     def gated_act(self, act, params, gate_up, out):
+        inter = out.shape[1]
+        if act == "gelu_tanh":
+            g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+            out.copy_((0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3))) * u).to(out.dtype))
+            return
         assert act == "clamped_swish"
         limit, slope = params
-        inter = out.shape[1]
         g = torch.clamp(gate_up[:, :inter].float(), max=limit)
         u = torch.clamp(gate_up[:, inter:].float(), -limit, limit)
         out.copy_((g * torch.sigmoid(slope * g) * (u + 1.0)).to(out.dtype))
@@ -264,17 +304,13 @@ class HostOps:
                 x = x * (1.0 / torch.sqrt((x * x).mean(-1, keepdim=True) + a["eps"])) * gain
             x = x.view(T, heads, dk)
             if a["inv_freq"] is not None:
-                half = a["rot_dims"] // 2
-                ang = positions.float()[:, None] * a["inv_freq"][None, :]
-                c, s = (torch.cos(ang) * a["amplitude"])[:, None, :], (torch.sin(ang) * a["amplitude"])[:, None, :]
-                u, v = x[..., :half], x[..., half:2 * half]
-                x = torch.cat([u * c - v * s, v * c + u * s, x[..., 2 * half:]], -1)
+                x = self._rotate(x, positions, a["inv_freq"], a["rot_dims"], bool(a.get("interleaved")), a["amplitude"])
             return x
         q = finish(a["q_in"], H, a["q_gain"], a.get("q_bias")).to(cache.dtype)
         a["q"][:T] = q.reshape(T, -1)
         if a["k_in"] is not None:
             k = finish(a["k_in"], G, a["k_gain"], a.get("k_bias")).to(cache.dtype)
-            v = biased(a["v_in"], a.get("v_bias")).reshape(T, G, dv)
+            v = biased(a["v_in"], a.get("v_bias")).reshape(T, G, dv).to(cache.dtype)
             for t in range(T):
                 slot = int(slot_mapping[t])
                 if slot >= 0:
@@ -293,6 +329,8 @@ class HostOps:
             vv = vals[pg, :, (js % ps).long()].float()
             for h in range(H):
                 s = (kk[:, h // rep] @ q[t, h].float()) * a["scale"]
+                if a.get("softcap"):
+                    s = a["softcap"] * torch.tanh(s / a["softcap"])
                 if a["sink"] is not None:
                     s = torch.cat([s, a["sink"][h:h + 1]])
                 w = torch.softmax(s, 0)[: js.numel()]
@@ -300,10 +338,15 @@ class HostOps:
 
     def moe_route(self, a, T):
         top, E = a["top_k"], a["logits"].shape[1]
-        s = torch.sigmoid(a["logits"][:T].float())
-        val, idx = torch.topk(s, top, dim=-1)
+        if a.get("mode", "sigmoid") == "softmax_chosen":
+            val, idx = torch.topk(a["logits"][:T].float(), top, dim=-1)
+            wt = torch.softmax(val, -1) * a["scale"]
+        else:
+            s = torch.sigmoid(a["logits"][:T].float())
+            val, idx = torch.topk(s, top, dim=-1)
+            wt = val / (val.sum(-1, keepdim=True) + 1e-20) * a["scale"]
         a["experts"][:T] = idx.to(torch.int32)
-        a["weights"][:T] = val / (val.sum(-1, keepdim=True) + 1e-20) * a["scale"]
+        a["weights"][:T] = wt
         flat = idx.reshape(-1)
         order = torch.argsort(flat, stable=True)
         a["order"][:T * top] = order.to(torch.int32)
@@ -385,6 +428,10 @@ class HostPlan:
                 o.recurrence(a, batch)
             elif k == "gated_norm":
                 o.gated_norm(a, T)
+            elif k == "row_norm":
+                o.row_norm(a, T)
+            elif k == "exp_gates":
+                o.exp_gates(a, batch)
             elif k == "linear_swiglu":
                 o.linear(a["x"][:T], a["w_gate_up"], a["gate_up"][:T])
                 if a.get("act", "silu") == "silu":
@@ -405,7 +452,10 @@ class HostPlan:
                 top = a["weights"].shape[1]
                 y = a["y"][:T * top].view(T, top, -1)
                 v = (a["weights"][:T, :, None] * y).sum(1)
-                a["out"][:T] = v if a["base"] is None else a["base"][:T] + v
+                base = a["base"][:T] if a["base"] is not None else None
+                if base is not None and a.get("base_gate") is not None:
+                    base = base * torch.sigmoid(a["base_gate"][:T])
+                a["out"][:T] = v if base is None else base + v
             elif k == "qkv_post":
                 self._qkv_post(a, batch, T)
             elif k == "attend":
@@ -422,11 +472,14 @@ class HostPlan:
                 o.linear(a["x"][:T], a["w"], a["mid"][:T])
                 o.activation(a["act"], a["params"], a["mid"][:T], a["out"][:T])
             elif k == "pointwise":
-                o.pointwise(a["what"], a["a"][:T], cut(a["b"]), a["out"][:T], a.get("scale", 1.0))
+                o.pointwise(a["what"], a["a"][:T], cut(a["b"]), a["out"][:T], a.get("scale", 1.0), a.get("group", 1))
             elif k == "batched_linear":
                 o.batched_linear(a["x"][:T], a["w"], a["out"][:T])
             elif k == "residual_add":
-                a["x"][:T] += a["a"][:T].float() + (a["b"][:T].float() if a["b"] is not None else 0.0)
+                u = a["a"][:T].float() * (a["a_scale"] if a.get("a_scale") is not None else 1.0)
+                if a["b"] is not None:
+                    u = u + a["b"][:T].float() * (a["b_scale"] if a.get("b_scale") is not None else 1.0)
+                a["x"][:T] += u
             elif k == "latent_attention":
                 g = batch.groups[a["group"]]
                 o.latent_attention(a, T, batch.positions, batch.token_request, g.block_tables, g.slot_mapping, g.page_size)
