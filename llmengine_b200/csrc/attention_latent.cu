@@ -2,7 +2,8 @@
 // share.  A head's query has already been carried into the latent space, so its score against a token is the dot
 // product with that row, and its output is the weighted sum of the rows' first `rank` values.  An optional sink per
 // head joins the softmax denominator with exp(sink_h): the running maximum starts at sink_h and the running sum at
-// one, with no value behind it.
+// one, with no value behind it.  With a window W a query sees only the last W keys, its own included; pages the window
+// has passed are never read.
 //
 // The plain kernel below visits keys one at a time, one warp per (token, head), for any sizes and both types; it is
 // the whole latent attention of the 32-bit path and the twin that the faster kernels are checked against.
@@ -32,7 +33,8 @@ __global__ void latent_attention_plain_kernel(LlmeLatentAttnArgs a) {
         acc[i] = 0.0f;
     }
     float m = a.sink ? a.sink[h] : -INFINITY, l = a.sink ? 1.0f : 0.0f;
-    for (int j = 0; j <= p; ++j) {
+    const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;     // the first key the window reaches
+    for (int j = lo; j <= p; ++j) {
         const int page = bt[j / ps];
         const T* row = (const T*)a.cache + ((size_t)page * ps + (j - (j / ps) * ps)) * width;
         float s = 0.0f, v[REGS];
@@ -81,7 +83,7 @@ LLME_API int llme_latent_attention_plain(const LlmeLatentAttnArgs* args, int dty
     const LlmeLatentAttnArgs& a = *args;
     if (a.tokens <= 0) return 0;
     if (!a.q || !a.cache || !a.out || !a.positions || !a.token_request || !a.block_tables) LLME_REFUSE("latent attention: null pointer");
-    if (a.nh <= 0 || a.rank <= 0 || a.rot < 0 || a.page_size <= 0 || a.max_blocks <= 0) LLME_REFUSE("latent attention: non-positive size");
+    if (a.nh <= 0 || a.rank <= 0 || a.rot < 0 || a.page_size <= 0 || a.max_blocks <= 0 || a.window < 0) LLME_REFUSE("latent attention: non-positive size");
     if (a.nh > 65535) LLME_REFUSE("latent attention: more than 65535 heads");
     if (dtype == LLME_F32) return launch_plain<float>(a, stream);
     if (dtype == LLME_BF16) return launch_plain<__nv_bfloat16>(a, stream);

@@ -12,7 +12,8 @@
 //      values of the same key rows (ldmatrix.trans), so nothing is loaded twice.
 // Keys arrive through a two-stage cp.async pipeline, page by page through the block table; rows outside the
 // needed range are zero-filled, never read.  The running maximum of a row starts at its head's sink (and the
-// running sum at one) when the mixer has one.  A decode step may split the keys of a request over several blocks,
+// running sum at one) when the mixer has one.  With a window W a query sees only the last W keys: a tile's walk starts
+// at the tile that holds the nearest key any of its rows sees.  A decode step may split the keys of a request over several blocks,
 // whose partial sums meet in scratch memory and are merged by a second kernel.
 #include "common.cuh"
 #include "kernel_args.h"
@@ -60,6 +61,7 @@ struct Args {
     float* scratch;
     int max_blocks, nh, rot, page_size, splits;
     float scale;
+    int window;                                    // W > 0: query i sees key j only if i - j < W
 };
 
 // RG groups of 16 query rows, WG = 8 / RG warps per group, key tiles of BN.
@@ -90,9 +92,12 @@ __global__ void __launch_bounds__(WARPS * 32, RG <= 2 ? 2 : 1) latent_attention_
     const int ctx = a.ctx_lens[r], first_pos = ctx - q_len;
     const int last_row = min(row0 + BM, n_rows) - 1;
     const int pmax = first_pos + last_row / H;                           // the farthest key any row of the tile sees
-    const int tiles = pmax / BN + 1;
+    const int W = a.window;
+    const int pmin = first_pos + row0 / H;                               // the position of the tile's first row
+    const int kmin = (W > 0 && pmin - W + 1 > 0) ? pmin - W + 1 : 0;     // the nearest key any row of the tile sees
+    const int tile_lo = kmin / BN, tiles = pmax / BN + 1 - tile_lo;
     // the tiles are dealt out evenly: with more ranges than tiles the later ranges get one tile each or none
-    const int t_begin = (int)((long long)split * tiles / a.splits), t_end = (int)((long long)(split + 1) * tiles / a.splits);
+    const int t_begin = tile_lo + (int)((long long)split * tiles / a.splits), t_end = tile_lo + (int)((long long)(split + 1) * tiles / a.splits);
     const int* bt = a.block_tables + (size_t)a.table_rows[r] * a.max_blocks;
     const int ps = a.page_size;
     const int chunks = width >> 3;                                       // 16-byte pieces of a row
@@ -115,7 +120,7 @@ __global__ void __launch_bounds__(WARPS * 32, RG <= 2 ? 2 : 1) latent_attention_
         for (int kr = warp; kr < BN; kr += WARPS) {
             const int j = j0 + kr;
             __nv_bfloat16* d = dst + (size_t)kr * ld;
-            if (j <= pmax) {
+            if (j <= pmax && j >= kmin) {                        // (a page the window has passed may be gone: never read)
                 const int blk = j / ps;
                 const __nv_bfloat16* src = a.cache + ((size_t)bt[blk] * ps + (j - blk * ps)) * width;
                 for (int c = lane; c < chunks; c += 32) cp_async16(d + c * 8, src + c * 8);
@@ -221,10 +226,10 @@ __global__ void __launch_bounds__(WARPS * 32, RG <= 2 ? 2 : 1) latent_attention_
 #pragma unroll
         for (int nt = 0; nt < NT_S; ++nt) {
             const int j = jbase + nt * 8;
-            s[nt][0] = j <= p0 ? s[nt][0] * a.scale : -INFINITY;
-            s[nt][1] = j + 1 <= p0 ? s[nt][1] * a.scale : -INFINITY;
-            s[nt][2] = j <= p1 ? s[nt][2] * a.scale : -INFINITY;
-            s[nt][3] = j + 1 <= p1 ? s[nt][3] * a.scale : -INFINITY;
+            s[nt][0] = j <= p0 && (W <= 0 || p0 - j < W) ? s[nt][0] * a.scale : -INFINITY;
+            s[nt][1] = j + 1 <= p0 && (W <= 0 || p0 - j - 1 < W) ? s[nt][1] * a.scale : -INFINITY;
+            s[nt][2] = j <= p1 && (W <= 0 || p1 - j < W) ? s[nt][2] * a.scale : -INFINITY;
+            s[nt][3] = j + 1 <= p1 && (W <= 0 || p1 - j - 1 < W) ? s[nt][3] * a.scale : -INFINITY;
             t0 = fmaxf(t0, fmaxf(s[nt][0], s[nt][1]));
             t1 = fmaxf(t1, fmaxf(s[nt][2], s[nt][3]));
         }
@@ -431,7 +436,7 @@ LLME_API int llme_latent_attention_tc(const LlmeFastAttnArgs* f, const float* si
     if (splits > 1 && (max_q_len != 1 || !f->scratch)) LLME_REFUSE("latent attention: splits need single tokens and scratch memory");
     if (f->n_rows > 65535 || splits > 64) LLME_REFUSE("latent attention: too many requests or splits for one launch");
     Args a = {(const __nv_bfloat16*)f->q, (const __nv_bfloat16*)f->cache, (__nv_bfloat16*)f->out, sink, f->rows, f->cu_q_lens, f->ctx_lens,
-              f->table_rows, f->block_tables, f->scratch, f->max_blocks, f->nh, rot, f->page_size, splits, f->scale};
+              f->table_rows, f->block_tables, f->scratch, f->max_blocks, f->nh, rot, f->page_size, splits, f->scale, f->window};
     int rc;
     if ((long long)max_q_len * f->nh <= 16) rc = launch<1, 64>(a, f->n_rows, max_q_len, stream);
     else if ((long long)max_q_len * f->nh <= 32) rc = launch<2, 64>(a, f->n_rows, max_q_len, stream);

@@ -13,25 +13,29 @@ LLME_API const char* llme_last_error() { return llme_error_buffer(); }
 // ----------------------------------------------------------------------------- norm, rotation, cache write
 // One value of a projection row after the norm (x * rinv * gain) and the rotation of its head's first `dims`
 // coordinates in rotate-half pairs (i, i + dims/2) by position * inv_freq[i], cosine and sine times `amp`.
+// `interleaved`: the pairs are (2i, 2i + 1) instead.
 template <typename T>
 __device__ __forceinline__ float finished_value(const T* __restrict__ row, const float* __restrict__ gain, float rinv, int head, int d, int dk,
-                                                const float* __restrict__ inv_freq, int dims, float amp, int position) {
+                                                const float* __restrict__ inv_freq, int dims, float amp, int position, int interleaved) {
     const int base = head * dk;
     auto normed = [&](int j) -> float {
         const float v = to_f32(row[base + j]);
         return gain ? (v * rinv) * gain[base + j] : v;
     };
     if (!inv_freq || d >= dims) return normed(d);
-    const int half = dims >> 1, i = d < half ? d : d - half;
+    const int half = dims >> 1, i = interleaved ? d >> 1 : (d < half ? d : d - half);
     float s, c;
     sincosf((float)position * inv_freq[i], &s, &c);
     s *= amp;
     c *= amp;
-    const float u = normed(i), w = normed(i + half);
-    return d < half ? u * c - w * s : w * c + u * s;
+    const float u = normed(interleaved ? 2 * i : i), w = normed(interleaved ? 2 * i + 1 : i + half);
+    const bool first = interleaved ? !(d & 1) : d < half;
+    return first ? u * c - w * s : w * c + u * s;
 }
 
-template <typename T>
+// I: the type of the projections (that of everything else, or 32-bit where they come from a convolution); T: the type of the
+// finished queries and of the cache.
+template <typename I, typename T>
 __global__ void window_post_kernel(LlmeWindowPostArgs a) {
     pdl_launch_dependents();
     pdl_wait();
@@ -39,7 +43,7 @@ __global__ void window_post_kernel(LlmeWindowPostArgs a) {
     const int t = blockIdx.x, dk = a.dk, dv = a.dv, ps = a.page_size;
     const int pos = a.positions[t];
     const int qn = a.nh * dk, kn = a.nkv * dk, vn = a.nkv * dv;
-    const T* q = (const T*)a.q_in + (size_t)t * a.q_stride;
+    const I* q = (const I*)a.q_in + (size_t)t * a.q_stride;
     float rq = 1.0f, rk = 1.0f;
     if (a.q_gain) {
         float ss = 0.0f;
@@ -51,11 +55,11 @@ __global__ void window_post_kernel(LlmeWindowPostArgs a) {
     }
     T* qo = (T*)a.q_out + (size_t)t * qn;
     for (int j = threadIdx.x; j < qn; j += blockDim.x)
-        qo[j] = from_f32<T>(finished_value(q, a.q_gain, rq, j / dk, j % dk, dk, a.inv_freq, a.rot_dims, a.amplitude, pos));
+        qo[j] = from_f32<T>(finished_value(q, a.q_gain, rq, j / dk, j % dk, dk, a.inv_freq, a.rot_dims, a.amplitude, pos, a.interleaved));
     const int slot = (a.cache && a.slot_mapping) ? a.slot_mapping[t] : -1;
     if (!a.k_in || slot < 0) return;                    // uniform over the block
-    const T* k = (const T*)a.k_in + (size_t)t * a.k_stride;
-    const T* v = (const T*)a.v_in + (size_t)t * a.v_stride;
+    const I* k = (const I*)a.k_in + (size_t)t * a.k_stride;
+    const I* v = (const I*)a.v_in + (size_t)t * a.v_stride;
     if (a.k_gain) {
         float ss = 0.0f;
         for (int j = threadIdx.x; j < kn; j += blockDim.x) {
@@ -69,11 +73,11 @@ __global__ void window_post_kernel(LlmeWindowPostArgs a) {
     T* vpage = kpage + (size_t)a.nkv * ps * dk;
     for (int j = threadIdx.x; j < kn; j += blockDim.x) {
         const int g = j / dk, d = j - g * dk;
-        kpage[((size_t)g * ps + off) * dk + d] = from_f32<T>(finished_value(k, a.k_gain, rk, g, d, dk, a.inv_freq, a.rot_dims, a.amplitude, pos));
+        kpage[((size_t)g * ps + off) * dk + d] = from_f32<T>(finished_value(k, a.k_gain, rk, g, d, dk, a.inv_freq, a.rot_dims, a.amplitude, pos, a.interleaved));
     }
     for (int j = threadIdx.x; j < vn; j += blockDim.x) {
         const int g = j / dv, d = j - g * dv;
-        vpage[((size_t)g * ps + off) * dv + d] = v[j];
+        vpage[((size_t)g * ps + off) * dv + d] = from_f32<T>(to_f32(v[j]));
     }
 }
 
@@ -82,7 +86,8 @@ __global__ void window_post_kernel(LlmeWindowPostArgs a) {
 // The value may be the key's own projection (v_in = k_in): it is stored as projected, with its bias, before the norm.
 template <typename T>
 __device__ __forceinline__ void finish_head(const T* __restrict__ in, const float* __restrict__ bias, const float* __restrict__ gain, float eps, int dk,
-                                            const float* __restrict__ inv_freq, int dims, float amp, int position, T* __restrict__ out, int lane) {
+                                            const float* __restrict__ inv_freq, int dims, float amp, int position, T* __restrict__ out, int lane,
+                                            int interleaved) {
     auto raw = [&](int j) -> float {
         const float v = to_f32(in[j]);
         return bias ? to_f32(from_f32<T>(v + bias[j])) : v;      // a projection's output has the type of the products
@@ -102,13 +107,13 @@ __device__ __forceinline__ void finish_head(const T* __restrict__ in, const floa
         float v;
         if (!inv_freq || d >= dims) v = normed(d);
         else {
-            const int i = d < half ? d : d - half;
+            const int i = interleaved ? d >> 1 : (d < half ? d : d - half);
             float s, c;
             sincosf((float)position * inv_freq[i], &s, &c);
             s *= amp;
             c *= amp;
-            const float u = normed(i), w = normed(i + half);
-            v = d < half ? u * c - w * s : w * c + u * s;
+            const float u = normed(interleaved ? 2 * i : i), w = normed(interleaved ? 2 * i + 1 : i + half);
+            v = (interleaved ? !(d & 1) : d < half) ? u * c - w * s : w * c + u * s;
         }
         out[d] = from_f32<T>(v);
     }
@@ -127,7 +132,7 @@ __global__ void window_post_heads_kernel(LlmeWindowPostArgs a) {
     const int dk = a.dk, dv = a.dv, ps = a.page_size, pos = a.positions[t];
     if (hh < a.nh) {
         finish_head((const T*)a.q_in + (size_t)t * a.q_stride + hh * dk, a.q_bias ? a.q_bias + hh * dk : nullptr, a.q_gain, a.eps, dk,
-                    a.inv_freq, a.rot_dims, a.amplitude, pos, (T*)a.q_out + ((size_t)t * a.nh + hh) * dk, lane);
+                    a.inv_freq, a.rot_dims, a.amplitude, pos, (T*)a.q_out + ((size_t)t * a.nh + hh) * dk, lane, a.interleaved);
         return;
     }
     const int slot = a.slot_mapping[t];
@@ -137,7 +142,7 @@ __global__ void window_post_heads_kernel(LlmeWindowPostArgs a) {
     if (hh < a.nh + a.nkv) {
         const int g = hh - a.nh;
         finish_head((const T*)a.k_in + (size_t)t * a.k_stride + g * dk, a.k_bias ? a.k_bias + g * dk : nullptr, a.k_gain, a.eps, dk,
-                    a.inv_freq, a.rot_dims, a.amplitude, pos, kpage + ((size_t)g * ps + off) * dk, lane);
+                    a.inv_freq, a.rot_dims, a.amplitude, pos, kpage + ((size_t)g * ps + off) * dk, lane, a.interleaved);
         return;
     }
     const int g = hh - a.nh - a.nkv;
@@ -156,7 +161,9 @@ LLME_API int llme_window_post(const LlmeWindowPostArgs* args, int dtype, cudaStr
     if (a.inv_freq && (a.rot_dims <= 0 || a.rot_dims % 2 || a.rot_dims > a.dk))
         LLME_REFUSE("window_post: %d rotated coordinates of %d need an even count", a.rot_dims, a.dk);
     if ((a.q_gain || a.k_gain) && !(a.eps > 0.0f)) LLME_REFUSE("window_post: eps must be positive");
+    const bool wide_in = a.in_f32 && dtype != LLME_F32;     // 32-bit projections, everything else in the type of the products
     if (a.head_norm || a.q_bias || a.k_bias || a.v_bias) {
+        if (wide_in) LLME_REFUSE("window_post: 32-bit projections come without biases and without the norm per head");
         if (!a.head_norm && (a.q_gain || a.k_gain)) LLME_REFUSE("window_post: biases come with the norm per head or with no norm");
         const long long items = (long long)a.tokens * (a.nh + (a.k_in ? 2 * a.nkv : 0));
         const int wpb = 4;
@@ -167,8 +174,9 @@ LLME_API int llme_window_post(const LlmeWindowPostArgs* args, int dtype, cudaStr
     }
     const int qn = a.nh * a.dk;
     const int threads = qn >= 2048 ? 512 : (qn >= 512 ? 256 : 128);
-    if (dtype == LLME_F32) llme_launch(window_post_kernel<float>, dim3(a.tokens), dim3(threads), 0, stream, a);
-    else if (dtype == LLME_BF16) llme_launch(window_post_kernel<__nv_bfloat16>, dim3(a.tokens), dim3(threads), 0, stream, a);
+    if (dtype == LLME_F32) llme_launch(window_post_kernel<float, float>, dim3(a.tokens), dim3(threads), 0, stream, a);
+    else if (dtype == LLME_BF16 && wide_in) llme_launch(window_post_kernel<float, __nv_bfloat16>, dim3(a.tokens), dim3(threads), 0, stream, a);
+    else if (dtype == LLME_BF16) llme_launch(window_post_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(a.tokens), dim3(threads), 0, stream, a);
     else LLME_REFUSE("window_post: unsupported dtype %d", dtype);
     LLME_LAUNCH_STATUS();
 }
@@ -215,6 +223,7 @@ __global__ void window_attention_plain_kernel(LlmeWindowAttnArgs a) {
             if (d < dk) s += q[i] * to_f32(kp[d]);
         }
         s = warp_sum(s) * a.scale;
+        if (a.softcap > 0.0f) s = a.softcap * tanhf(s / a.softcap);
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);       // exp(-inf) = 0 on the first key
         const float e = expf(s - m_new);

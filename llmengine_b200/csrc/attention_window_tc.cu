@@ -7,7 +7,7 @@
 // that hold the request's kept first positions, then the chunks of the window.  A row of a chunk that no query of the
 // tile can see is zero-filled and never read, so a page that was given back is never touched.  Each of the four warps
 // owns 16 rows: S = Q K^T with the queries kept in registers, the mask (j <= i and (i - j < window or j < keep_first)),
-// an online softmax whose running maximum starts at the sink and whose sum starts at one (the sink's own term), and
+// an optional cap on the scores (s <- c tanh(s / c)), an online softmax whose running maximum starts at the sink and whose sum starts at one (the sink's own term), and
 // O += P V with the probabilities taken straight from the score registers.
 //
 // Single decoded tokens: a request's chunks are dealt out to `splits` blocks (a window of a thousand keys is seventeen
@@ -141,7 +141,8 @@ __global__ void __launch_bounds__(THREADS) window_tc_kernel(LlmeWindowFastArgs a
         pos[h] = start + (valid[h] ? row / G : 0);
     }
     const float LOG2E = 1.4426950408889634f;
-    const float sc = a.scale * LOG2E;
+    const float cap = a.softcap, cap2 = cap * LOG2E;      // with a cap c: s <- c tanh(scale s / c), then to base 2
+    const float sc = cap > 0.0f ? a.scale / cap : a.scale * LOG2E;
     float m[2], l[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -194,7 +195,7 @@ __global__ void __launch_bounds__(THREADS) window_tc_kernel(LlmeWindowFastArgs a
             for (int n = 0; n < BN / 8; ++n)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    s[n][i] *= sc;
+                    s[n][i] = cap > 0.0f ? cap2 * tanhf(s[n][i] * sc) : s[n][i] * sc;
                     mx[i >> 1] = fmaxf(mx[i >> 1], s[n][i]);
                 }
         } else {
@@ -205,7 +206,7 @@ __global__ void __launch_bounds__(THREADS) window_tc_kernel(LlmeWindowFastArgs a
                     const int h = i >> 1;
                     const int j = j0 + n * 8 + (lane & 3) * 2 + (i & 1);
                     const bool see = valid[h] && j <= pos[h] && (W <= 0 || pos[h] - j < W || j < a.keep_first);
-                    const float v = see ? s[n][i] * sc : -INFINITY;
+                    const float v = see ? (cap > 0.0f ? cap2 * tanhf(s[n][i] * sc) : s[n][i] * sc) : -INFINITY;
                     s[n][i] = v;
                     mx[h] = fmaxf(mx[h], v);
                 }

@@ -99,6 +99,19 @@ __device__ __forceinline__ float clamped_swish_mul_bf16(float g, float u, float 
     return (g * __frcp_rn(1.0f + __expf(-slope * g))) * (u + 1.0f);
 }
 
+// gelu(g) u with the tanh form of gelu, for values that have been through bfloat16 and go back to it:
+// 0.5 g (1 + tanh(z)) = g / (1 + exp(-2 z)) with z = sqrt(2/pi) (g + 0.044715 g^3).
+__device__ __forceinline__ float gelu_tanh_mul_bf16(float g, float u) {
+    const float z = 0.7978845608028654f * fmaf(0.044715f * g * g, g, g);
+    return (g * __frcp_rn(1.0f + __expf(-2.0f * z))) * u;
+}
+
+// The gated activations by their code (LLME_GATE_*: 0 silu, 1 the clamped gate with p0 = limit and p1 = slope, 2 gelu in its
+// tanh form), in a product's epilogue.
+__device__ __forceinline__ float gated_mul_bf16(int act, float g, float u, float p0, float p1) {
+    return act == 1 ? clamped_swish_mul_bf16(g, u, p0, p1) : (act == 2 ? gelu_tanh_mul_bf16(g, u) : silu_mul_bf16(g, u));
+}
+
 // xIELU with its two coefficients already formed: z > 0: a_pos z^2 + z/2; z <= 0: a_neg (exp(z) - 1 - z) + z/2.
 __device__ __forceinline__ float xielu(float z, float a_pos, float a_neg) {
     return z > 0.0f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);

@@ -67,6 +67,11 @@ typedef int (*ShortConvFn)(const LlmeShortConvArgs*, int, cudaStream_t);
 typedef int (*RotateFn)(const LlmeRotateArgs*, cudaStream_t);
 typedef int (*RecurrenceFn)(const LlmeRecurrenceArgs*, cudaStream_t);
 typedef int (*GatedNormFn)(const LlmeGatedNormArgs*, cudaStream_t);
+typedef int (*SigmoidMulGroupedFn)(const void*, long long, const void*, long long, void*, long long, int, int, int, float, int, cudaStream_t);
+typedef int (*ResidualAddScaledFn)(float*, const void*, const void*, int, void*, int, int, int, const float*, const float*, cudaStream_t);
+typedef int (*MoeCombineGatedFn)(const float*, long long, const float*, const float*, float*, int, int, int, const float*, long long, cudaStream_t);
+typedef int (*RowNormFn)(const void*, long long, int, const void*, int, void*, long long, int, int, int, float, cudaStream_t);
+typedef int (*ExpGatesFn)(const LlmeExpGatesArgs*, cudaStream_t);
 typedef int (*GemmF32BatchedFn)(const float*, const void*, int, float*, int, int, int, long long, long long, long long, int, long long,
                                 long long, long long, cudaStream_t);
 
@@ -182,6 +187,8 @@ size_t record_size(int kind) {
         case LLME_OP_ROTATE: return sizeof(LlmeRotateOp);
         case LLME_OP_RECURRENCE: return sizeof(LlmeRecurrenceOp);
         case LLME_OP_GATED_NORM: return sizeof(LlmeGatedNormOp);
+        case LLME_OP_ROW_NORM: return sizeof(LlmeRowNormOp);
+        case LLME_OP_EXP_GATES: return sizeof(LlmeExpGatesOp);
     }
     return 0;
 }
@@ -189,8 +196,8 @@ const char* kind_name(int kind) {
     static const char* names[] = {"?", "embedding", "rmsnorm", "linear", "linear_swiglu", "qkv_post", "attend", "attention", "call",
                                   "linear_act", "pointwise", "batched_linear", "residual_add", "latent_attention", "token_side",
                                   "postnorm", "window_attention", "moe_route", "grouped_linear", "moe_combine", "short_conv", "rotate",
-                                  "recurrence", "gated_norm"};
-    return kind >= 1 && kind <= 23 ? names[kind] : names[0];
+                                  "recurrence", "gated_norm", "row_norm", "exp_gates"};
+    return kind >= 1 && kind <= 25 ? names[kind] : names[0];
 }
 
 constexpr int SKINNY_ROWS = 16;      // most rows the weight-streaming product takes (gemm_skinny.cu)
@@ -534,6 +541,11 @@ int op_linear_act(LlmeExecutor& ex, const LlmeLinearActOp& o, const LlmeStep& s,
 int op_pointwise(LlmeExecutor& ex, const LlmePointwiseOp& o, const LlmeStep& s, cudaStream_t st) {
     if (s.num_tokens <= 0) return 0;
     if (o.what != LLME_POINTWISE_SIGMOID_MUL) return ex.fail("pointwise: unknown operation %d", o.what);
+    if (o.group > 1) {
+        auto* g = (SigmoidMulGroupedFn)ex.find("sigmoid_mul_grouped");
+        if (!g) return ex.fail("no sigmoid_mul kernel with one gate per group of columns is registered");
+        return ex.launched(g(o.a, o.lda, o.b, o.ldb, o.out, o.ldo, o.dtype, s.num_tokens, o.cols, o.scale, o.group, st), "sigmoid_mul");
+    }
     if (o.scale != 1.0f) {
         auto* g = (SigmoidMulScaledFn)ex.find("sigmoid_mul_scaled");
         if (!g) return ex.fail("no scaled sigmoid_mul kernel is registered");
@@ -570,6 +582,11 @@ int op_batched_linear(LlmeExecutor& ex, const LlmeBatchedLinearOp& o, const Llme
 }
 
 int op_residual_add(LlmeExecutor& ex, const LlmeResidualAddOp& o, const LlmeStep& s, cudaStream_t st) {
+    if (o.a_scale || o.b_scale) {
+        auto* g = (ResidualAddScaledFn)ex.find("residual_add_scaled");
+        if (!g) return ex.fail("no residual_add kernel with scale vectors is registered");
+        return ex.launched(g(o.x, o.a, o.b, o.dtype, nullptr, 0, s.num_tokens, o.size, o.a_scale, o.b_scale, st), "residual_add");
+    }
     auto* f = (ResidualAddFn)ex.find("residual_add");
     if (!f) return ex.fail("no residual_add kernel is registered");
     return ex.launched(f(o.x, o.a, o.b, o.dtype, nullptr, 0, s.num_tokens, o.size, st), "residual_add");
@@ -577,7 +594,8 @@ int op_residual_add(LlmeExecutor& ex, const LlmeResidualAddOp& o, const LlmeStep
 
 // Key ranges per request for single tokens over a latent cache: as many blocks as the GPU has SMs, no range shorter
 // than two key tiles, at most 32.  A request's heads are one tile of rows per 32 heads.
-int latent_splits(const LlmeExecutor& ex, int requests, int nh, long long max_ctx) {
+int latent_splits(const LlmeExecutor& ex, int requests, int nh, long long max_ctx, int window) {
+    if (window > 0 && max_ctx > window) max_ctx = window;      // a token reads no more keys than its window holds
     const long long row_tiles = (nh + 31) / 32, bn = nh <= 32 ? 64 : 32;
     const long long tiles = (max_ctx + bn - 1) / bn;
     long long s = ex.sms / (requests * row_tiles);
@@ -596,7 +614,7 @@ int op_latent_attention(LlmeExecutor& ex, const LlmeLatentAttentionOp& o, const 
     p.kv_in = o.kv_in; p.kv_stride = o.kv_stride; p.q_rot = o.q_rot; p.q_rot_stride = o.q_rot_stride; p.q_rot_head_stride = o.q_rot_head_stride;
     p.c_gain = o.c_gain; p.gain_dtype = o.gain_dtype; p.eps = o.eps; p.inv_freq = o.inv_freq; p.rot_dims = o.rot_dims;
     p.positions = s.positions; p.q = o.q; p.cache = o.cache; p.slot_mapping = g.slot_mapping;
-    p.tokens = s.num_tokens; p.nh = o.nh; p.rank = o.rank; p.rot = o.rot;
+    p.tokens = s.num_tokens; p.nh = o.nh; p.rank = o.rank; p.rot = o.rot; p.interleaved = o.interleaved;
     if (int rc = ex.launched(post(&p, o.dtype, st), "latent_post")) return rc;
     // bfloat16 with a latent size the tensor-core kernel is built for: prompt portions in one launch, single tokens in
     // another whose requests may be cut into several key ranges
@@ -606,14 +624,14 @@ int op_latent_attention(LlmeExecutor& ex, const LlmeLatentAttentionOp& o, const 
         LlmeFastAttnArgs f = {};
         f.q = o.q; f.cache = o.cache; f.out = o.out; f.cu_q_lens = s.cu_q_lens; f.ctx_lens = s.ctx_lens; f.table_rows = s.state_slots;
         f.block_tables = g.block_tables; f.scratch = o.scratch; f.max_blocks = g.max_blocks; f.nh = o.nh; f.nkv = 1;
-        f.page_size = g.page_size; f.scale = o.scale;
+        f.page_size = g.page_size; f.scale = o.scale; f.window = o.window;
         if (s.num_portion > 0) {
             f.rows = s.portion_rows; f.n_rows = s.num_portion; f.splits = 1;
             if (int rc = ex.launched(tc(&f, o.sink, o.rot, s.max_portion_len, st), "latent_attention_tc")) return rc;
         }
         if (s.num_decode > 0) {
             f.rows = s.decode_rows; f.n_rows = s.num_decode;
-            f.splits = latent_splits(ex, s.num_decode, o.nh, s.max_decode_ctx);
+            f.splits = latent_splits(ex, s.num_decode, o.nh, s.max_decode_ctx, o.window);
             if (f.splits > 1 && (!o.scratch || (long long)s.num_decode * f.splits * o.nh * (o.rank + 2) > o.scratch_floats)) f.splits = 1;
             if (int rc = ex.launched(tc(&f, o.sink, o.rot, 1, st), "latent_attention_tc")) return rc;
             if (f.splits > 1) ++ex.launches;
@@ -623,7 +641,7 @@ int op_latent_attention(LlmeExecutor& ex, const LlmeLatentAttentionOp& o, const 
     auto* plain = (LatentAttnPlainFn)ex.find("latent_attention_plain");
     if (!plain) return ex.fail("no latent attention kernel is registered");
     LlmeLatentAttnArgs a = {o.q, o.cache, o.out, o.sink, s.positions, s.token_request, g.block_tables, g.max_blocks, s.num_tokens,
-                            o.nh, o.rank, o.rot, g.page_size, o.scale};
+                            o.nh, o.rank, o.rot, g.page_size, o.scale, o.window};
     return ex.launched(plain(&a, o.dtype, st), "latent_attention_plain");
 }
 
@@ -665,6 +683,7 @@ int op_window_attention(LlmeExecutor& ex, const LlmeWindowAttentionOp& o, const 
     p.positions = s.positions; p.q_out = o.q; p.cache = o.cache; p.slot_mapping = g.slot_mapping;
     p.tokens = s.num_tokens; p.nh = o.nh; p.nkv = o.nkv; p.dk = o.dk; p.dv = o.dv; p.page_size = g.page_size;
     p.q_bias = o.q_bias; p.k_bias = o.k_bias; p.v_bias = o.v_bias; p.head_norm = o.head_norm;
+    p.interleaved = o.interleaved; p.in_f32 = o.in_f32;
     if (int rc = ex.launched(post(&p, o.dtype, st), "window_post")) return rc;
     // bfloat16 with sizes the tensor-core kernel is built for: prompt portions in one launch, single tokens in another
     auto* tc = (WindowAttnTcFn)ex.find("window_attention_tc/" + std::to_string(o.dk) + "x" + std::to_string(o.dv));
@@ -672,7 +691,7 @@ int op_window_attention(LlmeExecutor& ex, const LlmeWindowAttentionOp& o, const 
         LlmeWindowFastArgs f = {};
         f.q = o.q; f.cache = o.cache; f.out = o.out; f.sink = o.sink; f.cu_q_lens = s.cu_q_lens; f.ctx_lens = s.ctx_lens;
         f.table_rows = s.state_slots; f.block_tables = g.block_tables; f.max_blocks = g.max_blocks; f.nh = o.nh; f.nkv = o.nkv;
-        f.page_size = g.page_size; f.window = o.window; f.keep_first = o.keep_first; f.scale = o.scale;
+        f.page_size = g.page_size; f.window = o.window; f.keep_first = o.keep_first; f.scale = o.scale; f.softcap = o.softcap;
         if (s.num_portion > 0) {
             f.rows = s.portion_rows; f.n_rows = s.num_portion;
             if (int rc = ex.launched(tc(&f, s.max_portion_len, 0, st), "window_attention_tc")) return rc;
@@ -696,7 +715,7 @@ int op_window_attention(LlmeExecutor& ex, const LlmeWindowAttentionOp& o, const 
     auto* plain = (WindowAttnPlainFn)ex.find("window_attention_plain");
     if (!plain) return ex.fail("no window attention kernel is registered");
     LlmeWindowAttnArgs a = {o.q, o.cache, o.out, o.sink, s.positions, s.token_request, g.block_tables, g.max_blocks, s.num_tokens,
-                            o.nh, o.nkv, o.dk, o.dv, g.page_size, o.window, o.keep_first, o.scale};
+                            o.nh, o.nkv, o.dk, o.dv, g.page_size, o.window, o.keep_first, o.scale, o.softcap};
     return ex.launched(plain(&a, o.dtype, st), "window_attention_plain");
 }
 
@@ -729,7 +748,8 @@ int op_recurrence(LlmeExecutor& ex, const LlmeRecurrenceOp& o, const LlmeStep& s
     if (!f) return ex.fail("no recurrence kernel is registered");
     LlmeRecurrenceArgs a = {o.q, o.k, o.ldq, o.ldk, o.qk_groups, o.v, o.ldv, o.v_dtype, o.gate, o.decay, o.dt, o.lddt, o.dt_dtype, o.dt_bias,
                             o.a_log, o.skip, o.state, o.state_stride, o.out, o.ldo, s.cu_q_lens, s.state_slots, s.num_requests, o.heads,
-                            o.n, o.p, o.scratch, o.scratch_floats, s.num_tokens, s.max_portion_len > 1 ? s.max_portion_len : 1};
+                            o.n, o.p, o.scratch, o.scratch_floats, s.num_tokens, s.max_portion_len > 1 ? s.max_portion_len : 1,
+                            o.keep, o.take, o.ld_gates, o.unit_column};
     return ex.launched(f(&a, st), "recurrence");
 }
 
@@ -737,15 +757,32 @@ int op_gated_norm(LlmeExecutor& ex, const LlmeGatedNormOp& o, const LlmeStep& s,
     if (s.num_tokens <= 0) return 0;
     auto* f = (GatedNormFn)ex.find("gated_norm");
     if (!f) return ex.fail("no gated_norm kernel is registered");
-    LlmeGatedNormArgs a = {o.y, o.ldy, o.gate, o.ldg, o.weight, o.out, o.ldo, o.dtype, s.num_tokens, o.cols, o.group, o.gate_first, o.eps, o.scale};
+    LlmeGatedNormArgs a = {o.y, o.ldy, o.gate, o.ldg, o.weight, o.out, o.ldo, o.dtype, s.num_tokens, o.cols, o.group, o.gate_first, o.eps, o.scale,
+                           o.gate_act, o.floor, o.ld_floor, o.den_eps};
     return ex.launched(f(&a, st), "gated_norm");
+}
+
+int op_row_norm(LlmeExecutor& ex, const LlmeRowNormOp& o, const LlmeStep& s, cudaStream_t st) {
+    if (s.num_tokens <= 0) return 0;
+    auto* f = (RowNormFn)ex.find("row_norm");
+    if (!f) return ex.fail("no row_norm kernel is registered");
+    return ex.launched(f(o.x, o.ldx, o.x_dtype, o.gain, o.gain_dtype, o.out, o.ldo, o.out_dtype, s.num_tokens, o.cols, o.eps, st), "row_norm");
+}
+
+int op_exp_gates(LlmeExecutor& ex, const LlmeExpGatesOp& o, const LlmeStep& s, cudaStream_t st) {
+    if (s.num_tokens <= 0 || s.num_requests <= 0) return 0;
+    auto* f = (ExpGatesFn)ex.find("exp_gates");
+    if (!f) return ex.fail("no exp_gates kernel is registered");
+    LlmeExpGatesArgs a = {o.i_pre, o.f_pre, o.ld_pre, o.cap, o.state, o.state_stride, o.keep, o.take, o.floor, o.ld_out, s.cu_q_lens, s.state_slots,
+                          s.num_requests, o.heads};
+    return ex.launched(f(&a, st), "exp_gates");
 }
 
 int op_moe_route(LlmeExecutor& ex, const LlmeMoeRouteOp& o, const LlmeStep& s, cudaStream_t st) {
     if (s.num_tokens <= 0) return 0;
     auto* f = (MoeRouteFn)ex.find("moe_route");
     if (!f) return ex.fail("no moe_route kernel is registered");
-    LlmeMoeRouteArgs a = {o.logits, o.ld, s.num_tokens, o.num_experts, o.top_k, o.scale, o.experts, o.weights, o.offsets, o.order, o.counts};
+    LlmeMoeRouteArgs a = {o.logits, o.ld, s.num_tokens, o.num_experts, o.top_k, o.scale, o.experts, o.weights, o.offsets, o.order, o.counts, o.mode};
     const int rc = ex.launched(f(&a, st), "moe_route");
     ++ex.launches;                                          // routing and ordering are two kernels
     return rc;
@@ -766,6 +803,11 @@ int op_grouped_linear(LlmeExecutor& ex, const LlmeGroupedLinearOp& o, const Llme
 }
 
 int op_moe_combine(LlmeExecutor& ex, const LlmeMoeCombineOp& o, const LlmeStep& s, cudaStream_t st) {
+    if (o.base_gate) {
+        auto* g = (MoeCombineGatedFn)ex.find("moe_combine_gated");
+        if (!g) return ex.fail("no moe_combine kernel with a gate on the shared part is registered");
+        return ex.launched(g(o.y, o.ldy, o.weights, o.base, o.out, s.num_tokens, o.top_k, o.size, o.base_gate, o.ld_gate, st), "moe_combine");
+    }
     auto* f = (MoeCombineFn)ex.find("moe_combine");
     if (!f) return ex.fail("no moe_combine kernel is registered");
     return ex.launched(f(o.y, o.ldy, o.weights, o.base, o.out, s.num_tokens, o.top_k, o.size, st), "moe_combine");
@@ -924,6 +966,8 @@ LLME_EXPORT int llme_plan_run(LlmePlan* p, const LlmeStep* step, int first, int 
             case LLME_OP_ROTATE: rc = op_rotate(ex, *(const LlmeRotateOp*)b, s, stream); break;
             case LLME_OP_RECURRENCE: rc = op_recurrence(ex, *(const LlmeRecurrenceOp*)b, s, stream); break;
             case LLME_OP_GATED_NORM: rc = op_gated_norm(ex, *(const LlmeGatedNormOp*)b, s, stream); break;
+            case LLME_OP_ROW_NORM: rc = op_row_norm(ex, *(const LlmeRowNormOp*)b, s, stream); break;
+            case LLME_OP_EXP_GATES: rc = op_exp_gates(ex, *(const LlmeExpGatesOp*)b, s, stream); break;
             case LLME_OP_CALL: {
                 const LlmeCallOp& c = *(const LlmeCallOp*)b;
                 rc = c.fn ? c.fn(c.user, step, stream) : 0;

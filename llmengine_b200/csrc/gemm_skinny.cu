@@ -176,7 +176,7 @@ __global__ void __launch_bounds__(THREADS, BLOCKS) gemm_skinny_kernel(SkinnyArgs
                 const float g = __bfloat162float(__float2bfloat16_rn(total(tok * 16 + j)));
                 const float up = __bfloat162float(__float2bfloat16_rn(total(tok * 16 + j + 8)));
                 reinterpret_cast<O*>(a.out)[(size_t)tok * a.ldo + col] =
-                    from_f32<O>(a.pointwise == 1 ? clamped_swish_mul_bf16(g, up, a.p0, a.p1) : silu_mul_bf16(g, up));
+                    from_f32<O>(gated_mul_bf16(a.pointwise, g, up, a.p0, a.p1));
             }
         }
     }
@@ -255,12 +255,12 @@ LLME_API int llme_gemm_skinny_swiglu_bf16(const void* x, long long ldx, const vo
     LLME_REFUSE("gemm_skinny: unsupported output dtype %d", out_dtype);
 }
 
-// out[M, inter] = act(x Wg^T, x Wu^T) with W = [Wg | Wu]: act 0 = silu(g) u; act 1 = the clamped gate, p0 = limit, p1 = slope.
+// out[M, inter] = act(x Wg^T, x Wu^T) with W = [Wg | Wu]: act 0 = silu(g) u; act 1 = the clamped gate, p0 = limit, p1 = slope; act 2 = gelu(g) u, the tanh form.
 LLME_API int llme_gemm_skinny_gated_bf16(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
                                          long long ldo, int M, int inter, int K, int act, float p0, float p1, cudaStream_t stream) {
     if (M <= 0 || inter <= 0) return 0;
     if (!x || !w || !out) LLME_REFUSE("gemm_skinny: null pointer");
-    if (act != 0 && act != 1) LLME_REFUSE("gemm_skinny: unknown gated activation %d", act);
+    if (act < 0 || act > 2) LLME_REFUSE("gemm_skinny: unknown gated activation %d", act);
     if (inter > (1 << 29) || !llme_gemm_skinny_supports(M, 2 * inter, K, ldx, ldw)) LLME_REFUSE("gemm_skinny: M=%d inter=%d K=%d ldx=%lld ldw=%lld is not supported (M <= 16, K and strides multiples of 8)", M, inter, K, ldx, ldw);
     if (((uintptr_t)x | (uintptr_t)w) % 16) LLME_REFUSE("gemm_skinny: operands must be 16-byte aligned");
     if (ldo < inter) LLME_REFUSE("gemm_skinny: output row stride shorter than the row");

@@ -230,7 +230,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& map_x, const CUt
                         for (int j = 0; j < 32; ++j) {
                             const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[j])));
                             const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[j])));
-                            v[j] = __float_as_uint(a.pointwise == 1 ? clamped_swish_mul_bf16(g, u, a.p0, a.p1) : silu_mul_bf16(g, u));
+                            v[j] = __float_as_uint(gated_mul_bf16(a.pointwise, g, u, a.p0, a.p1));
                         }
                     } else {
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -458,13 +458,13 @@ LLME_API int llme_gemm_tc_swiglu_bf16(const void* x, long long ldx, const void* 
     return launch_act<256, 4, bf16, false>(x, ldx, w, ldw, a, stream);
 }
 
-// out[M, inter] (bfloat16) = act(x Wg^T, x Wu^T): act 0 = silu(g) u; act 1 = the clamped gate, p0 = limit, p1 = slope.
+// out[M, inter] (bfloat16) = act(x Wg^T, x Wu^T): act 0 = silu(g) u; act 1 = the clamped gate, p0 = limit, p1 = slope; act 2 = gelu(g) u, the tanh form.
 LLME_API int llme_gemm_tc_gated_bf16(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype, long long ldo,
                                      int M, int inter, int K, int act, float p0, float p1, cudaStream_t stream) {
     if (M <= 0 || inter <= 0) return 0;
     if (!x || !w || !out) LLME_REFUSE("gemm_tc: null pointer");
     if (out_dtype != LLME_BF16) LLME_REFUSE("gemm_tc: the gated product writes bfloat16");
-    if (act != 0 && act != 1) LLME_REFUSE("gemm_tc: unknown gated activation %d", act);
+    if (act < 0 || act > 2) LLME_REFUSE("gemm_tc: unknown gated activation %d", act);
     if (!llme_gemm_tc_swiglu_supports(M, inter, K, ldx, ldw, ldo)) LLME_REFUSE("gemm_tc: M=%d inter=%d K=%d ldx=%lld ldw=%lld ldo=%lld is not supported (K and strides must be multiples of 8)", M, inter, K, ldx, ldw, ldo);
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) % 16) LLME_REFUSE("gemm_tc: operands and output must be 16-byte aligned");
     TcArgs a{out, ldo, M, 2 * inter, K, 0, 0, inter, act, p0, p1};

@@ -57,6 +57,7 @@ typedef struct LlmeLatentPostArgs {
     void* q;                                      /* [T, nh, rank + rot]: the last rot of every head are written */
     void* cache; const int* slot_mapping;         /* rows of rank + rot; slot < 0: not stored */
     int tokens, nh, rank, rot;
+    int interleaved;                              /* 1: the rotation pairs coordinate 2i with 2i + 1, not i with i + rot_dims / 2 */
 } LlmeLatentPostArgs;
 
 /* Attention over cached latent rows [c | rotated key part], one row per token for all heads. */
@@ -66,6 +67,7 @@ typedef struct LlmeLatentAttnArgs {
     const int* positions; const int* token_request; const int* block_tables;
     int max_blocks, tokens, nh, rank, rot, page_size;
     float scale;
+    int window;                                   /* W > 0: query i sees key j only if i - j < W */
 } LlmeLatentAttnArgs;
 
 /* Whole-projection norm, partial rotation and cache write for an attention whose keys and values differ in width
@@ -83,6 +85,8 @@ typedef struct LlmeWindowPostArgs {
      * [nkv * dk], [nkv * dv]); `head_norm` 1: every head is normed by itself and the gains are [dk], shared by the heads */
     const float* q_bias; const float* k_bias; const float* v_bias;
     int head_norm;
+    int interleaved;                                         /* 1: the rotation pairs coordinate 2i with 2i + 1, not i with i + rot_dims / 2 */
+    int in_f32;                                              /* 1: q_in, k_in and v_in are 32-bit whatever the type of q_out and the cache */
 } LlmeWindowPostArgs;
 
 /* Attention over such a cache: query i sees key j if j <= i and (i - j < window or j < keep_first). */
@@ -92,6 +96,7 @@ typedef struct LlmeWindowAttnArgs {
     const int* positions; const int* token_request; const int* block_tables;
     int max_blocks, tokens, nh, nkv, dk, dv, page_size, window, keep_first;
     float scale;
+    float softcap;                                           /* c > 0: a score s becomes c tanh(s / c) behind the scale */
 } LlmeWindowAttnArgs;
 
 /* The same for the tensor-core kernel: the requests `rows` of the batch, each with its tokens
@@ -103,6 +108,7 @@ typedef struct LlmeWindowFastArgs {
     int max_blocks, n_rows, nh, nkv, page_size, window, keep_first;
     float scale;
     float* scratch; int splits;      /* single tokens: each request's keys cut into `splits` ranges whose parts meet in `scratch` */
+    float softcap;                   /* c > 0: a score s becomes c tanh(s / c) behind the scale */
 } LlmeWindowFastArgs;
 
 /* Routing of a mixture of experts (csrc/moe.cu). */
@@ -111,6 +117,7 @@ typedef struct LlmeMoeRouteArgs {
     int tokens, num_experts, top_k; float scale;
     int* experts; float* weights;                            /* [T, top_k] */
     int* offsets; int* order; int* counts;                   /* [E + 1], [T * top_k], [E] (zero between launches) */
+    int mode;                                                /* 0: sigmoid scores normalised over the chosen; 1: softmax over the chosen logits */
 } LlmeMoeRouteArgs;
 
 /* One product per expert over the rows routed to it. */
@@ -164,6 +171,9 @@ typedef struct LlmeRecurrenceArgs {
     int requests, heads, n, p;
     float* scratch; long long scratch_floats;                /* room for the states of pieces of long requests, or NULL */
     int tokens, max_len;                                     /* of the step; the most tokens one request brings */
+    /* gate 2: a_t = keep[t, h], s_t = take[t, h], 32-bit, made by an earlier kernel (row stride ld_gates) */
+    const float* keep; const float* take; long long ld_gates;
+    int unit_column;                                         /* 1: column p - 1 has no v behind it, its v_t is one; v is [T, heads * (p - 1)] */
 } LlmeRecurrenceArgs;
 
 /* RMS norm in groups of `group` columns with a gate (silu of a second tensor) before or after it:
@@ -176,4 +186,20 @@ typedef struct LlmeGatedNormArgs {
     void* out; long long ldo;
     int dtype, tokens, cols, group, gate_first;
     float eps, scale;
+    int gate_act;                                            /* 0: silu(g); 1: sigmoid(g) */
+    /* with `floor` [T, cols / group] every group of y is one value wider than `group`: the extra value d stands behind the
+     * group's own, and the group is divided by max(|d|, floor) + den_eps before anything else */
+    const float* floor; long long ld_floor; float den_eps;
 } LlmeGatedNormArgs;
+
+/* The gates of a matrix memory with exponential gating (csrc/recurrent.cu), per request and head over the request's tokens:
+ * a_t = cap tanh(i_pre / cap), b_t = logsigmoid(cap tanh(f_pre / cap)) (cap 0: uncapped), M_t = max(b_t + M_(t-1), a_t) with M
+ * kept in the request's slot; keep = exp(b_t + M_(t-1) - M_t), take = exp(a_t - M_t), floor = exp(-M_t). */
+typedef struct LlmeExpGatesArgs {
+    const float* i_pre; const float* f_pre; long long ld_pre;   /* [T, heads] each */
+    float cap;
+    float* state; long long state_stride;                    /* slot s: [heads] at state + s * state_stride */
+    float* keep; float* take; float* floor; long long ld_out;   /* [T, heads] each */
+    const int* cu_q_lens; const int* state_slots;
+    int requests, heads;
+} LlmeExpGatesArgs;

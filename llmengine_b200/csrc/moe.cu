@@ -1,4 +1,5 @@
-// A mixture of experts: routing (sigmoid scores, the largest few chosen, weights normalised over the chosen), the list
+// A mixture of experts: routing (sigmoid scores, the largest few chosen, weights normalised over the chosen; or the
+// softmax over the chosen logits alone), the list
 // of (token, choice) pairs expert by expert, one product per expert over its pairs (plain form: any sizes, both types,
 // 32-bit FMA in a fixed order of k, so that a row never depends on what shares its tile), and the weighted sum of a
 // token's pairs in the order of its choices.  The tensor-core form of the grouped product is csrc/moe_tc.cu.
@@ -18,7 +19,7 @@ __global__ void moe_route_kernel(LlmeMoeRouteArgs a) {
     const float* z = a.logits + (size_t)t * a.ld;
     const int E = a.num_experts;
     unsigned taken = 0;                                   // bit i: this lane's i-th logit (lane + 32 i) is chosen
-    float total = 0.0f;
+    float total = 0.0f, first = 0.0f;
     float score[8];
     int chosen[8];
     for (int k = 0; k < a.top_k; ++k) {
@@ -36,7 +37,9 @@ __global__ void moe_route_kernel(LlmeMoeRouteArgs a) {
             if (oi >= 0 && (bi < 0 || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
         }
         if (bi >= 0 && (bi & 31) == lane) taken |= 1u << (bi >> 5);
-        const float s = 1.0f / (1.0f + expf(-best));
+        if (k == 0) first = best;
+        // mode 1: the softmax over the chosen logits alone, relative to the largest of them (the first chosen)
+        const float s = a.mode == 1 ? expf(best - first) : 1.0f / (1.0f + expf(-best));
         score[k & 7] = s;
         chosen[k & 7] = bi;
         total += s;
@@ -45,7 +48,7 @@ __global__ void moe_route_kernel(LlmeMoeRouteArgs a) {
             a.weights[(size_t)t * a.top_k + k] = s;
         }
     }
-    const float norm = a.scale / (total + 1e-20f);
+    const float norm = a.scale / (a.mode == 1 ? total : total + 1e-20f);
     if (lane == 0) {
         for (int k = 0; k < a.top_k; ++k) {
             const size_t at = (size_t)t * a.top_k + k;
@@ -87,6 +90,7 @@ LLME_API int llme_moe_route(const LlmeMoeRouteArgs* args, cudaStream_t stream) {
     const LlmeMoeRouteArgs& a = *args;
     if (a.tokens <= 0) return 0;
     if (!a.logits || !a.experts || !a.weights || !a.offsets || !a.order || !a.counts) LLME_REFUSE("moe_route: null pointer");
+    if (a.mode != 0 && a.mode != 1) LLME_REFUSE("moe_route: unknown mode %d", a.mode);
     if (a.num_experts <= 0 || a.num_experts > 1024 || a.top_k <= 0 || a.top_k > a.num_experts)
         LLME_REFUSE("moe_route: %d of %d experts (at most 1024)", a.top_k, a.num_experts);
     const int wpb = 4;
@@ -209,25 +213,35 @@ LLME_API int llme_grouped_linear(const LlmeGroupedArgs* args, int x_dtype, int w
 
 // ----------------------------------------------------------------------------- the weighted sum of a token's pairs
 __global__ void moe_combine_kernel(const float* __restrict__ y, long long ldy, const float* __restrict__ weights, const float* __restrict__ base,
-                                   float* __restrict__ out, int top_k, int cols) {
+                                   float* __restrict__ out, int top_k, int cols, const float* __restrict__ base_gate, long long ld_gate) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
+    const float share = base && base_gate ? 1.0f / (1.0f + expf(-base_gate[(size_t)t * ld_gate])) : 1.0f;   // the shared expert's gate
     for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < cols; j += gridDim.y * blockDim.x) {
         float v = 0.0f;
         for (int k = 0; k < top_k; ++k) v = fmaf(weights[(size_t)t * top_k + k], y[((size_t)t * top_k + k) * ldy + j], v);
-        out[(size_t)t * cols + j] = base ? base[(size_t)t * cols + j] + v : v;
+        out[(size_t)t * cols + j] = base ? base[(size_t)t * cols + j] * share + v : v;
     }
 }
 
+LLME_API int llme_moe_combine_gated(const float* y, long long ldy, const float* weights, const float* base, float* out, int tokens,
+                                    int top_k, int cols, const float* base_gate, long long ld_gate, cudaStream_t stream);
+
 LLME_API int llme_moe_combine(const float* y, long long ldy, const float* weights, const float* base, float* out, int tokens,
                               int top_k, int cols, cudaStream_t stream) {
+    return llme_moe_combine_gated(y, ldy, weights, base, out, tokens, top_k, cols, nullptr, 0, stream);
+}
+
+// The same with base[t] times sigmoid(base_gate[t * ld_gate]) (base_gate NULL: times one).
+LLME_API int llme_moe_combine_gated(const float* y, long long ldy, const float* weights, const float* base, float* out, int tokens,
+                                    int top_k, int cols, const float* base_gate, long long ld_gate, cudaStream_t stream) {
     if (tokens <= 0 || cols <= 0) return 0;
     if (!y || !weights || !out || top_k <= 0) LLME_REFUSE("moe_combine: null pointer or no choices");
     const int threads = 128;
     int pieces = (cols + threads - 1) / threads;
     const int wanted = (592 + tokens - 1) / tokens;
     if (pieces > wanted) pieces = wanted;
-    llme_launch(moe_combine_kernel, dim3(tokens, pieces < 1 ? 1 : pieces), dim3(threads), 0, stream, y, ldy, weights, base, out, top_k, cols);
+    llme_launch(moe_combine_kernel, dim3(tokens, pieces < 1 ? 1 : pieces), dim3(threads), 0, stream, y, ldy, weights, base, out, top_k, cols, base_gate, ld_gate);
     LLME_LAUNCH_STATUS();
 }

@@ -72,27 +72,34 @@ LLME_API int llme_xielu(const void* in, long long ld_in, void* out, long long ld
 }
 
 // ----------------------------------------------------------------------------- out = a * sigmoid(b) * scale
+// `group` > 1: b has one value for every `group` neighbouring columns of a (one gate per head).
 template <typename T>
 __global__ void sigmoid_mul_kernel(const T* __restrict__ a, long long lda, const T* __restrict__ b, long long ldb, T* __restrict__ out,
-                                   long long ldo, int cols, float scale) {
+                                   long long ldo, int cols, float scale, int group) {
     pdl_launch_dependents();
     pdl_wait();
     const T* ar = a + (size_t)blockIdx.x * lda;
     const T* br = b + (size_t)blockIdx.x * ldb;
     T* o = out + (size_t)blockIdx.x * ldo;
     for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < cols; j += gridDim.y * blockDim.x)
-        o[j] = from_f32<T>((to_f32(ar[j]) * sigmoid(to_f32(br[j]))) * scale);
+        o[j] = from_f32<T>((to_f32(ar[j]) * sigmoid(to_f32(br[group > 1 ? j / group : j]))) * scale);
+}
+
+LLME_API int llme_sigmoid_mul_grouped(const void* a, long long lda, const void* b, long long ldb, void* out, long long ldo, int dtype,
+                                      int rows, int cols, float scale, int group, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (!a || !b || !out) LLME_REFUSE("sigmoid_mul: null pointer");
+    if (group < 1 || cols % group) LLME_REFUSE("sigmoid_mul: %d columns are not whole groups of %d", cols, group);
+    const int threads = 128;
+    if (dtype == LLME_F32) llme_launch(sigmoid_mul_kernel<float>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const float*)a, lda, (const float*)b, ldb, (float*)out, ldo, cols, scale, group);
+    else if (dtype == LLME_BF16) llme_launch(sigmoid_mul_kernel<__nv_bfloat16>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb, (__nv_bfloat16*)out, ldo, cols, scale, group);
+    else LLME_REFUSE("sigmoid_mul: unsupported dtype %d", dtype);
+    LLME_LAUNCH_STATUS();
 }
 
 LLME_API int llme_sigmoid_mul_scaled(const void* a, long long lda, const void* b, long long ldb, void* out, long long ldo, int dtype,
                                      int rows, int cols, float scale, cudaStream_t stream) {
-    if (rows <= 0 || cols <= 0) return 0;
-    if (!a || !b || !out) LLME_REFUSE("sigmoid_mul: null pointer");
-    const int threads = 128;
-    if (dtype == LLME_F32) llme_launch(sigmoid_mul_kernel<float>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const float*)a, lda, (const float*)b, ldb, (float*)out, ldo, cols, scale);
-    else if (dtype == LLME_BF16) llme_launch(sigmoid_mul_kernel<__nv_bfloat16>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb, (__nv_bfloat16*)out, ldo, cols, scale);
-    else LLME_REFUSE("sigmoid_mul: unsupported dtype %d", dtype);
-    LLME_LAUNCH_STATUS();
+    return llme_sigmoid_mul_grouped(a, lda, b, ldb, out, ldo, dtype, rows, cols, scale, 1, stream);
 }
 
 LLME_API int llme_sigmoid_mul(const void* a, long long lda, const void* b, long long ldb, void* out, long long ldo, int dtype,
@@ -101,26 +108,37 @@ LLME_API int llme_sigmoid_mul(const void* a, long long lda, const void* b, long 
 }
 
 // ----------------------------------------------------------------------------- x += a (+ b), optionally a copy of x in another type
+// With `a_scale` / `b_scale` (vectors of the row's width) a contribution is multiplied by its vector first.
 template <typename A, typename C>
-__global__ void residual_add_kernel(float* __restrict__ x, const A* __restrict__ a, const A* __restrict__ b, C* __restrict__ copy, int cols) {
+__global__ void residual_add_kernel(float* __restrict__ x, const A* __restrict__ a, const A* __restrict__ b, C* __restrict__ copy, int cols,
+                                    const float* __restrict__ a_scale, const float* __restrict__ b_scale) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * cols;
     for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < cols; j += gridDim.y * blockDim.x) {
         float v = to_f32(a[base + j]);
-        if (b) v += to_f32(b[base + j]);
+        if (a_scale) v *= a_scale[j];
+        if (b) v += b_scale ? to_f32(b[base + j]) * b_scale[j] : to_f32(b[base + j]);
         v = x[base + j] + v;                 // the sublayers' contributions are summed first, then added to the stream
         x[base + j] = v;
         if (copy) copy[base + j] = from_f32<C>(v);
     }
 }
 
+LLME_API int llme_residual_add_scaled(float* x, const void* a, const void* b, int ab_dtype, void* copy, int copy_dtype, int rows, int cols,
+                                      const float* a_scale, const float* b_scale, cudaStream_t stream);
+
 LLME_API int llme_residual_add(float* x, const void* a, const void* b, int ab_dtype, void* copy, int copy_dtype, int rows, int cols,
                                cudaStream_t stream) {
+    return llme_residual_add_scaled(x, a, b, ab_dtype, copy, copy_dtype, rows, cols, nullptr, nullptr, stream);
+}
+
+LLME_API int llme_residual_add_scaled(float* x, const void* a, const void* b, int ab_dtype, void* copy, int copy_dtype, int rows, int cols,
+                                      const float* a_scale, const float* b_scale, cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return 0;
     if (!x || !a) LLME_REFUSE("residual_add: null pointer");
     const int threads = 128;
-#define LLME_RA(A, C) llme_launch(residual_add_kernel<A, C>, grid_for(rows, cols, threads), dim3(threads), 0, stream, x, (const A*)a, (const A*)b, (C*)copy, cols)
+#define LLME_RA(A, C) llme_launch(residual_add_kernel<A, C>, grid_for(rows, cols, threads), dim3(threads), 0, stream, x, (const A*)a, (const A*)b, (C*)copy, cols, a_scale, b_scale)
     if (ab_dtype == LLME_F32 && (copy_dtype == LLME_F32 || !copy)) LLME_RA(float, float);
     else if (ab_dtype == LLME_F32 && copy_dtype == LLME_BF16) LLME_RA(float, __nv_bfloat16);
     else if (ab_dtype == LLME_BF16 && (copy_dtype == LLME_BF16 || !copy)) LLME_RA(__nv_bfloat16, __nv_bfloat16);
@@ -189,15 +207,18 @@ LLME_API int llme_rmsnorm_add(float* x, const float* y, const void* gain, int ga
 // ----------------------------------------------------------------------------- latent: norm, rotation, cache write
 // One value of a vector whose first `dims` coordinates are rotated in rotate-half pairs (i, i + dims/2) by the angle
 // position * inv_freq[i], formed in 32-bit; coordinates from `dims` on pass unchanged.
+// `interleaved`: the pairs are (2i, 2i + 1) instead.
 template <typename T>
-__device__ __forceinline__ float rotated_value(const T* __restrict__ v, int idx, int dims, const float* __restrict__ inv_freq, int position) {
+__device__ __forceinline__ float rotated_value(const T* __restrict__ v, int idx, int dims, const float* __restrict__ inv_freq, int position,
+                                               int interleaved = 0) {
     if (idx >= dims) return to_f32(v[idx]);
-    const int half = dims >> 1, i = idx < half ? idx : idx - half;
+    const int half = dims >> 1, i = interleaved ? idx >> 1 : (idx < half ? idx : idx - half);
     const float angle = (float)position * inv_freq[i];
     float s, c;
     sincosf(angle, &s, &c);
-    const float u = to_f32(v[i]), w = to_f32(v[i + half]);
-    return idx < half ? u * c - w * s : w * c + u * s;
+    const float u = to_f32(v[interleaved ? 2 * i : i]), w = to_f32(v[interleaved ? 2 * i + 1 : i + half]);
+    const bool first = interleaved ? !(idx & 1) : idx < half;
+    return first ? u * c - w * s : w * c + u * s;
 }
 
 template <typename T, typename G>
@@ -220,7 +241,7 @@ __global__ void latent_post_kernel(LlmeLatentPostArgs a) {
         const float rinv = 1.0f / sqrtf(ss / (float)rank + a.eps);
         const G* gain = (const G*)a.c_gain;
         for (int j = threadIdx.x; j < rank; j += blockDim.x) row[j] = from_f32<T>((to_f32(kv[j]) * rinv) * to_f32(gain[j]));
-        for (int j = threadIdx.x; j < rot; j += blockDim.x) row[rank + j] = from_f32<T>(rotated_value(kv + rank, j, a.rot_dims, a.inv_freq, pos));
+        for (int j = threadIdx.x; j < rot; j += blockDim.x) row[rank + j] = from_f32<T>(rotated_value(kv + rank, j, a.rot_dims, a.inv_freq, pos, a.interleaved));
     }
     if (rot > 0 && a.q_rot && a.q && (gridDim.y == 1 || blockIdx.y > 0)) {
         const T* qr = (const T*)a.q_rot + (size_t)t * a.q_rot_stride;
@@ -228,7 +249,7 @@ __global__ void latent_post_kernel(LlmeLatentPostArgs a) {
         const int first = gridDim.y == 1 ? 0 : blockIdx.y - 1, stride = gridDim.y == 1 ? 1 : gridDim.y - 1;
         for (int e = first * blockDim.x + threadIdx.x; e < a.nh * rot; e += stride * blockDim.x) {
             const int h = e / rot, j = e - h * rot;
-            q[(size_t)h * width + rank + j] = from_f32<T>(rotated_value(qr + (size_t)h * a.q_rot_head_stride, j, a.rot_dims, a.inv_freq, pos));
+            q[(size_t)h * width + rank + j] = from_f32<T>(rotated_value(qr + (size_t)h * a.q_rot_head_stride, j, a.rot_dims, a.inv_freq, pos, a.interleaved));
         }
     }
 }
@@ -252,6 +273,50 @@ LLME_API int llme_latent_post(const LlmeLatentPostArgs* args, int dtype, cudaStr
     else if (dtype == LLME_BF16 && a.gain_dtype == LLME_F32) LLME_LP(__nv_bfloat16, float);
     else LLME_REFUSE("latent_post: unsupported dtypes %d / %d", dtype, a.gain_dtype);
 #undef LLME_LP
+    LLME_LAUNCH_STATUS();
+}
+
+// ----------------------------------------------------------------------------- out = x / sqrt(mean(x^2) + eps) * gain over strided rows
+// A norm on (a column range of) a product: one warp per row for rows of up to 1,024 values, a block per row beyond that.
+template <typename X, typename G, typename O>
+__global__ void row_norm_kernel(const X* __restrict__ x, long long ldx, const G* __restrict__ gain, O* __restrict__ out, long long ldo,
+                                int rows, int cols, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const bool by_warp = cols <= 1024;
+    const int lane = threadIdx.x & 31;
+    const long long r = by_warp ? (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5) : blockIdx.x;
+    if (r >= rows) return;                               // (uniform over a warp, and over the block where a block has one row)
+    const X* xr = x + (size_t)r * ldx;
+    O* o = out + (size_t)r * ldo;
+    const int first = by_warp ? lane : threadIdx.x, step = by_warp ? 32 : blockDim.x;
+    float ss = 0.0f;
+    for (int j = first; j < cols; j += step) {
+        const float v = to_f32(xr[j]);
+        ss += v * v;
+    }
+    ss = by_warp ? warp_sum(ss) : block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)cols + eps);
+    for (int j = first; j < cols; j += step) o[j] = from_f32<O>((to_f32(xr[j]) * rinv) * to_f32(gain[j]));
+}
+
+LLME_API int llme_row_norm(const void* x, long long ldx, int x_dtype, const void* gain, int gain_dtype, void* out, long long ldo, int out_dtype,
+                           int rows, int cols, float eps, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (!x || !gain || !out) LLME_REFUSE("row_norm: null pointer");
+    if (!(eps > 0.0f)) LLME_REFUSE("row_norm: eps must be positive");
+    const bool by_warp = cols <= 1024;
+    const dim3 grid(by_warp ? (rows + 3) / 4 : rows), block(by_warp ? 128 : 256);
+#define LLME_RN(X, G, O) llme_launch(row_norm_kernel<X, G, O>, grid, block, 0, stream, (const X*)x, ldx, (const G*)gain, (O*)out, ldo, rows, cols, eps)
+    typedef __nv_bfloat16 bf;
+    if (x_dtype == LLME_F32 && gain_dtype == LLME_F32 && out_dtype == LLME_F32) LLME_RN(float, float, float);
+    else if (x_dtype == LLME_BF16 && gain_dtype == LLME_BF16 && out_dtype == LLME_BF16) LLME_RN(bf, bf, bf);
+    else if (x_dtype == LLME_BF16 && gain_dtype == LLME_F32 && out_dtype == LLME_BF16) LLME_RN(bf, float, bf);
+    else if (x_dtype == LLME_F32 && gain_dtype == LLME_F32 && out_dtype == LLME_BF16) LLME_RN(float, float, bf);
+    else if (x_dtype == LLME_F32 && gain_dtype == LLME_BF16 && out_dtype == LLME_BF16) LLME_RN(float, bf, bf);
+    else LLME_REFUSE("row_norm: unsupported dtypes %d / %d / %d", x_dtype, gain_dtype, out_dtype);
+#undef LLME_RN
     LLME_LAUNCH_STATUS();
 }
 
@@ -372,13 +437,14 @@ LLME_API int llme_postnorm(float* x, const void* y, int y_dtype, const void* gai
 }
 
 // ----------------------------------------------------------------------------- out = act(gate, up), gate_up = [gate | up] by columns
-// act 0: g sigmoid(g) u.  act 1 (p0 = limit, p1 = slope): g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1).
+// act 0: g sigmoid(g) u.  act 2: gelu(g) u, the tanh form.  act 1 (p0 = limit, p1 = slope): g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1).
 __device__ __forceinline__ float gated_activation(int act, float g, float u, float p0, float p1) {
     if (act == 1) {
         g = fminf(g, p0);
         u = fminf(fmaxf(u, -p0), p0);
         return (g * sigmoid(p1 * g)) * (u + 1.0f);
     }
+    if (act == 2) return gelu_tanh(g) * u;
     return (g * sigmoid(g)) * u;
 }
 
@@ -403,7 +469,7 @@ LLME_API int llme_gated_act_bias(const void* gate_up, long long ld_in, void* out
                                  float p0, float p1, const float* bias, cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return 0;
     if (!gate_up || !out) LLME_REFUSE("gated_act: null pointer");
-    if (act != 0 && act != 1) LLME_REFUSE("gated_act: unknown activation %d", act);
+    if (act < 0 || act > 2) LLME_REFUSE("gated_act: unknown activation %d", act);
     const int threads = 128;
     if (dtype == LLME_F32) llme_launch(gated_act_kernel<float>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const float*)gate_up, ld_in, (float*)out, ld_out, cols, act, p0, p1, bias);
     else if (dtype == LLME_BF16) llme_launch(gated_act_kernel<__nv_bfloat16>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up, ld_in, (__nv_bfloat16*)out, ld_out, cols, act, p0, p1, bias);

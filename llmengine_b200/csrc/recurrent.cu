@@ -294,14 +294,18 @@ __global__ void __launch_bounds__(256) recurrence_column_kernel(LlmeRecurrenceAr
     const float rate = a.gate == 1 ? -expf(a.a_log[h]) : 0.0f;
     const float bias = a.gate == 1 && a.dt_bias ? a.dt_bias[h] : 0.0f;
     const float skip = a.skip ? a.skip[h] : 0.0f;
+    const int vp = a.unit_column ? p - 1 : p;                       // columns that have a v behind them
     for (int t = first; t < last; ++t) {
         const float* q = a.q + (size_t)t * a.ldq + (size_t)g * n;
         const float* k = a.k + (size_t)t * a.ldk + (size_t)g * n;
-        const float v = load_as_f32(a.v, a.v_dtype, (size_t)t * a.ldv + (size_t)h * p + j);
+        const float v = j < vp ? load_as_f32(a.v, a.v_dtype, (size_t)t * a.ldv + (size_t)h * vp + j) : 1.0f;
         float decay = fixed, step = 1.0f;
         if (a.gate == 1) {
             step = softplus32(load_as_f32(a.dt, a.dt_dtype, (size_t)t * a.lddt + h) + bias);
             decay = expf(rate * step);
+        } else if (a.gate == 2) {
+            decay = a.keep[(size_t)t * a.ld_gates + h];
+            step = a.take[(size_t)t * a.ld_gates + h];
         }
         float y = 0.0f;
 #pragma unroll
@@ -425,7 +429,8 @@ __global__ void __launch_bounds__(256, R <= 4 ? 3 : 1) recurrence_tile_kernel(Ll
     const float* qg = a.q + (size_t)g * n;
     const float* kg = a.k + (size_t)g * n;
 
-    float v_next[V_EACH], dt_next = 0.0f;
+    const int vp = a.unit_column ? p - 1 : p;                           // columns that have a v behind them
+    float v_next[V_EACH], dt_next = 0.0f, keep_next = 1.0f;
     // Sends for the tokens t0 .. t0 + TT - 1: q and k straight into buffer b, v and dt into registers for now.
     auto fetch = [&](int t0, int b) {
         if (vec) {
@@ -453,9 +458,14 @@ __global__ void __launch_bounds__(256, R <= 4 ? 3 : 1) recurrence_tile_kernel(Ll
 #pragma unroll
         for (int m = 0; m < V_EACH; ++m) {
             const int idx = tid + 256 * m, u = idx / REC_COLUMNS, c = idx % REC_COLUMNS, t = t0 + u;
-            v_next[m] = u < TT && t < last && jb + c < p ? load_as_f32(a.v, a.v_dtype, (size_t)t * a.ldv + (size_t)h * p + jb + c) : 0.0f;
+            v_next[m] = u < TT && t < last && jb + c < p
+                            ? (jb + c < vp ? load_as_f32(a.v, a.v_dtype, (size_t)t * a.ldv + (size_t)h * vp + jb + c) : 1.0f) : 0.0f;
         }
         dt_next = tid < TT && a.gate == 1 && t0 + tid < last ? load_as_f32(a.dt, a.dt_dtype, (size_t)(t0 + tid) * a.lddt + h) : 0.0f;
+        if (tid < TT && a.gate == 2 && t0 + tid < last) {
+            dt_next = a.take[(size_t)(t0 + tid) * a.ld_gates + h];
+            keep_next = a.keep[(size_t)(t0 + tid) * a.ld_gates + h];
+        }
     };
     // Completes buffer b; a token past the end gets what changes nothing: q = k = v = 0, step 0, decay 1.
     auto land = [&](int t0, int b) {
@@ -467,8 +477,8 @@ __global__ void __launch_bounds__(256, R <= 4 ? 3 : 1) recurrence_tile_kernel(Ll
         if (tid < TT) {
             float st = 0.0f, dc = 1.0f;
             if (t0 + tid < last) {
-                st = a.gate == 1 ? softplus32(dt_next + bias) : 1.0f;
-                dc = a.gate == 1 ? expf(rate * st) : fixed;
+                st = a.gate == 1 ? softplus32(dt_next + bias) : (a.gate == 2 ? dt_next : 1.0f);
+                dc = a.gate == 1 ? expf(rate * st) : (a.gate == 2 ? keep_next : fixed);
             }
             sm.step[b][tid] = st;
             sm.decay[b][tid] = dc;
@@ -633,7 +643,9 @@ LLME_API int llme_recurrence(const LlmeRecurrenceArgs* args, cudaStream_t stream
     if (a.requests <= 0) return 0;
     if (!a.q || !a.k || !a.v || !a.state || !a.out || !a.cu_q_lens || !a.state_slots) LLME_REFUSE("recurrence: null pointer");
     if (a.heads <= 0 || a.n <= 0 || a.p <= 0 || a.qk_groups <= 0 || a.heads % a.qk_groups) LLME_REFUSE("recurrence: %d heads in %d groups", a.heads, a.qk_groups);
-    if (a.gate == 0 ? !a.decay : (a.gate != 1 || !a.dt || !a.a_log)) LLME_REFUSE("recurrence: gate %d lacks its constants", a.gate);
+    if (a.gate == 0 ? !a.decay : a.gate == 1 ? (!a.dt || !a.a_log) : (a.gate != 2 || !a.keep || !a.take))
+        LLME_REFUSE("recurrence: gate %d lacks its constants", a.gate);
+    if (a.unit_column && (a.p < 2 || a.skip)) LLME_REFUSE("recurrence: a column without v stands beside others and has no skip");
     if (a.n > 512) LLME_REFUSE("recurrence: a state of %d rows per column, this build takes up to 512", a.n);
     if (a.heads > 65535 || a.requests > 65535) LLME_REFUSE("recurrence: too many heads or requests for one launch");
     if (a.max_len <= 1 || a.p < 4) {                                    // single tokens, or too few columns for four a warp
@@ -666,7 +678,66 @@ LLME_API int llme_recurrence(const LlmeRecurrenceArgs* args, cudaStream_t stream
     LLME_LAUNCH_STATUS();
 }
 
+// ----------------------------------------------------------------------------- exponential gates with a running maximum
+// One warp per (request, head), 32 tokens at a time: every lane forms the two log gates of its token (the transcendental
+// part, side by side), then all lanes walk the 32 running maxima in the tokens' order (an addition and a maximum each, the
+// operands handed round the warp), and every lane forms its token's three outputs.  The walk is the plain one, so a token's
+// values do not depend on how its request was cut into steps.
+__device__ __forceinline__ float log_sigmoid32(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
+
+__global__ void exp_gates_kernel(LlmeExpGatesArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), r = blockIdx.y;
+    if (h >= a.heads) return;
+    const int first = a.cu_q_lens[r], last = a.cu_q_lens[r + 1];
+    if (last <= first) return;
+    float* kept = a.state + (size_t)a.state_slots[r] * a.state_stride + h;
+    float M = *kept;
+    for (int t0 = first; t0 < last; t0 += 32) {
+        const int t = t0 + lane;
+        float ga = 0.0f, gb = 0.0f;
+        if (t < last) {
+            ga = a.i_pre[(size_t)t * a.ld_pre + h];
+            gb = a.f_pre[(size_t)t * a.ld_pre + h];
+            if (a.cap > 0.0f) {
+                ga = a.cap * tanhf(ga / a.cap);
+                gb = a.cap * tanhf(gb / a.cap);
+            }
+            gb = log_sigmoid32(gb);
+        }
+        float before = M, after = M;
+        const int count = min(32, last - t0);
+        for (int u = 0; u < count; ++u) {
+            const float au = __shfl_sync(0xffffffffu, ga, u), bu = __shfl_sync(0xffffffffu, gb, u);
+            const float next = fmaxf(bu + M, au);
+            if (u == lane) { before = M; after = next; }
+            M = next;
+        }
+        if (t < last) {
+            a.keep[(size_t)t * a.ld_out + h] = expf(gb + before - after);
+            a.take[(size_t)t * a.ld_out + h] = expf(ga - after);
+            a.floor[(size_t)t * a.ld_out + h] = expf(-after);
+        }
+    }
+    if (lane == 0) *kept = M;
+}
+
+LLME_API int llme_exp_gates(const LlmeExpGatesArgs* args, cudaStream_t stream) {
+    const LlmeExpGatesArgs& a = *args;
+    if (a.requests <= 0 || a.heads <= 0) return 0;
+    if (!a.i_pre || !a.f_pre || !a.state || !a.keep || !a.take || !a.floor || !a.cu_q_lens || !a.state_slots) LLME_REFUSE("exp_gates: null pointer");
+    if (a.cap < 0.0f) LLME_REFUSE("exp_gates: a negative cap");
+    if (a.requests > 65535) LLME_REFUSE("exp_gates: too many requests for one launch");
+    const int warps = a.heads >= 4 ? 4 : a.heads;
+    llme_launch(exp_gates_kernel, dim3((a.heads + warps - 1) / warps, a.requests), dim3(32 * warps), 0, stream, a);
+    LLME_LAUNCH_STATUS();
+}
+
 // ----------------------------------------------------------------------------- grouped RMS norm with a silu gate
+__device__ __forceinline__ float gate32(float z, int act) { return act == 1 ? 1.0f / (1.0f + expf(-z)) : silu32(z); }
+
 template <typename T>
 __global__ void gated_norm_kernel(LlmeGatedNormArgs a) {
     pdl_launch_dependents();
@@ -675,19 +746,22 @@ __global__ void gated_norm_kernel(LlmeGatedNormArgs a) {
     const int groups = a.cols / a.group;
     const long long item = (long long)blockIdx.x * warps + (threadIdx.x >> 5);      // (token, group)
     if (item >= (long long)a.tokens * groups) return;
-    const int t = (int)(item / groups), c0 = (int)(item - (long long)t * groups) * a.group;
-    const float* y = a.y + (size_t)t * a.ldy + c0;
+    const int t = (int)(item / groups), gi = (int)(item - (long long)t * groups), c0 = gi * a.group;
+    const float* y = a.y + (size_t)t * a.ldy + (a.floor ? c0 + gi : c0);       // with a floor every group of y is one value wider
     const T* g = (const T*)a.gate + (size_t)t * a.ldg + c0;
     T* o = (T*)a.out + (size_t)t * a.ldo + c0;
+    const float den = a.floor ? fmaxf(fabsf(y[a.group]), a.floor[(size_t)t * a.ld_floor + gi]) + a.den_eps : 1.0f;
     float ss = 0.0f;
     for (int c = lane; c < a.group; c += 32) {
-        const float u = a.gate_first ? y[c] * silu32(to_f32(g[c])) : y[c];
+        const float yc = a.floor ? y[c] / den : y[c];
+        const float u = a.gate_first ? yc * gate32(to_f32(g[c]), a.gate_act) : yc;
         ss += u * u;
     }
     const float rinv = 1.0f / sqrtf(warp_sum(ss) / (float)a.group + a.eps);
     for (int c = lane; c < a.group; c += 32) {
-        const float gate = silu32(to_f32(g[c]));
-        float u = (a.gate_first ? y[c] * gate : y[c]) * rinv;
+        const float gate = gate32(to_f32(g[c]), a.gate_act);
+        const float yc = a.floor ? y[c] / den : y[c];
+        float u = (a.gate_first ? yc * gate : yc) * rinv;
         if (a.weight) u *= a.weight[c0 + c];
         if (!a.gate_first) u *= gate;
         o[c] = from_f32<T>(u * a.scale);
@@ -703,20 +777,21 @@ __global__ void __launch_bounds__(128) gated_norm_block_kernel(LlmeGatedNormArgs
     pdl_launch_dependents();
     pdl_wait();
     const int groups = a.cols / a.group;
-    const int t = blockIdx.x / groups, c0 = (blockIdx.x - t * groups) * a.group;
-    const float* y = a.y + (size_t)t * a.ldy + c0;
+    const int t = blockIdx.x / groups, gi = blockIdx.x - t * groups, c0 = gi * a.group;
+    const float* y = a.y + (size_t)t * a.ldy + (a.floor ? c0 + gi : c0);
     const T* g = (const T*)a.gate + (size_t)t * a.ldg + c0;
     T* o = (T*)a.out + (size_t)t * a.ldo + c0;
+    const float den = a.floor ? fmaxf(fabsf(y[a.group]), a.floor[(size_t)t * a.ld_floor + gi]) + a.den_eps : 1.0f;
     float u[8], gate[8], ss = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int c = threadIdx.x + blockDim.x * i;
-        u[i] = c < a.group ? y[c] : 0.0f;
+        u[i] = c < a.group ? (a.floor ? y[c] / den : y[c]) : 0.0f;
         gate[i] = c < a.group ? to_f32(g[c]) : 0.0f;
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        gate[i] = silu32(gate[i]);
+        gate[i] = gate32(gate[i], a.gate_act);
         if (a.gate_first) u[i] *= gate[i];
         ss += u[i] * u[i];
     }

@@ -69,13 +69,14 @@ enum LlmeOpKind {
     LLME_OP_EMBEDDING = 1, LLME_OP_RMSNORM, LLME_OP_LINEAR, LLME_OP_LINEAR_SWIGLU, LLME_OP_QKV_POST, LLME_OP_ATTEND,
     LLME_OP_ATTENTION, LLME_OP_CALL, LLME_OP_LINEAR_ACT, LLME_OP_POINTWISE, LLME_OP_BATCHED_LINEAR, LLME_OP_RESIDUAL_ADD,
     LLME_OP_LATENT_ATTENTION, LLME_OP_TOKEN_SIDE, LLME_OP_POSTNORM, LLME_OP_WINDOW_ATTENTION, LLME_OP_MOE_ROUTE,
-    LLME_OP_GROUPED_LINEAR, LLME_OP_MOE_COMBINE, LLME_OP_SHORT_CONV, LLME_OP_ROTATE, LLME_OP_RECURRENCE, LLME_OP_GATED_NORM
+    LLME_OP_GROUPED_LINEAR, LLME_OP_MOE_COMBINE, LLME_OP_SHORT_CONV, LLME_OP_ROTATE, LLME_OP_RECURRENCE, LLME_OP_GATED_NORM,
+    LLME_OP_ROW_NORM, LLME_OP_EXP_GATES
 };
 
 enum { LLME_ACT_XIELU = 1 };
 /* activations of a (gate, up) pair: g sigmoid(g) u; with p0 = limit, p1 = slope: g' = min(g, limit),
  * u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1) */
-enum { LLME_GATE_SILU = 0, LLME_GATE_CLAMPED_SWISH = 1 };
+enum { LLME_GATE_SILU = 0, LLME_GATE_CLAMPED_SWISH = 1, LLME_GATE_GELU_TANH = 2 };   /* 2: gelu(g) u, the tanh form of gelu */
 enum { LLME_POINTWISE_SIGMOID_MUL = 1 };
 
 enum { LLME_ROWS_TOKENS = 0, LLME_ROWS_LOGITS = 1 };
@@ -150,13 +151,15 @@ typedef struct LlmeLinearActOp {
     int act; float p0, p1;
 } LlmeLinearActOp;
 
-/* Elementwise over the step's rows.  LLME_POINTWISE_SIGMOID_MUL: out = a * sigmoid(b) * scale. */
+/* Elementwise over the step's rows.  LLME_POINTWISE_SIGMOID_MUL: out = a * sigmoid(b) * scale; with group > 1, b has one
+ * value for every `group` neighbouring columns of a. */
 typedef struct LlmePointwiseOp {
     int what, dtype, cols;
     const void* a; long long lda;
     const void* b; long long ldb;
     void* out; long long ldo;
     float scale;
+    int group;
 } LlmePointwiseOp;
 
 /* out[t, b, :] = w[b] x[t, b, :] for b < batch: one small matrix per member (a head). */
@@ -167,9 +170,10 @@ typedef struct LlmeBatchedLinearOp {
     int batch, n, k;
 } LlmeBatchedLinearOp;
 
-/* x += a (+ b): contributions that no following norm adds. */
+/* x += a (+ b): contributions that no following norm adds; each times its vector [size] first, where it has one. */
 typedef struct LlmeResidualAddOp {
     float* x; const void* a; const void* b; int dtype; int size;
+    const float* a_scale; const float* b_scale;
 } LlmeResidualAddOp;
 
 /* Attention over cached latent rows [c | rotated key part] shared by all heads (csrc/attention_latent.cu), from the
@@ -184,6 +188,8 @@ typedef struct LlmeLatentAttentionOp {
     int nh, rank, rot; float scale;
     const float* sink;                                        /* [nh] or NULL */
     float* scratch; long long scratch_floats;
+    int window;                                               /* W > 0: query i sees key j only if i - j < W */
+    int interleaved;                                          /* 1: the rotation pairs coordinate 2i with 2i + 1 */
 } LlmeLatentAttentionOp;
 
 /* x += a (+ b); e = table[token][offset .. offset + dim); g = gelu_tanh(w_gate x) * e; y = w_proj g;
@@ -221,6 +227,9 @@ typedef struct LlmeWindowAttentionOp {
     /* options (off when zero): biases of the projections, added first; head_norm 1: every head is normed by itself and the
      * gains are [dk], shared by the heads.  v_in may be k_in itself: the values are then the keys as projected. */
     const float* q_bias; const float* k_bias; const float* v_bias; int head_norm;
+    float softcap;                                           /* c > 0: a score s becomes c tanh(s / c) behind the scale */
+    int interleaved;                                         /* 1: the rotation pairs coordinate 2i with 2i + 1 */
+    int in_f32;                                              /* 1: q_in, k_in, v_in are 32-bit whatever `dtype` is (they come from a convolution) */
 } LlmeWindowAttentionOp;
 
 /* Routing of a mixture of experts: s = sigmoid(logits), the top_k largest, w_e = scale * s_e / (sum of the chosen s + 1e-20);
@@ -228,6 +237,7 @@ typedef struct LlmeWindowAttentionOp {
 typedef struct LlmeMoeRouteOp {
     const float* logits; long long ld; int num_experts, top_k; float scale;
     int* experts; float* weights; int* offsets; int* order; int* counts;
+    int mode;                  /* 0: as above; 1: the largest logits chosen, w_e = scale * softmax over the chosen logits alone */
 } LlmeMoeRouteOp;
 
 /* One product per expert over the pairs routed to it. */
@@ -240,9 +250,10 @@ typedef struct LlmeGroupedLinearOp {
     int num_experts, top_k, n, k, gather, scatter, act;       /* act 1: w[e] = [gate | up], out = silu(gate) * up */
 } LlmeGroupedLinearOp;
 
-/* out[t] = base[t] + sum_k weights[t, k] y[t top_k + k]. */
+/* out[t] = base[t] (times sigmoid(base_gate[t * ld_gate]) where base_gate is given) + sum_k weights[t, k] y[t top_k + k]. */
 typedef struct LlmeMoeCombineOp {
     const float* y; long long ldy; const float* weights; const float* base; float* out; int top_k, size;
+    const float* base_gate; long long ld_gate;
 } LlmeMoeCombineOp;
 
 /* Causal convolution per channel over each request's tokens, y_t = bias + sum_j w[:, K-1-j] x_(t-j), then silu (act 1);
@@ -277,6 +288,9 @@ typedef struct LlmeRecurrenceOp {
     float* out; long long ldo;
     int heads, n, p;
     float* scratch; long long scratch_floats;                /* lets long portions run in pieces side by side, or NULL */
+    /* gate 2: a_t = keep[t, h], s_t = take[t, h] (32-bit, row stride ld_gates), made by an earlier record */
+    const float* keep; const float* take; long long ld_gates;
+    int unit_column;                                         /* 1: column p - 1 has no v behind it, its v_t is one; v is [T, heads (p - 1)] */
 } LlmeRecurrenceOp;
 
 /* RMS norm in groups of `group` columns with a silu gate: gate_first 1: u = y silu(g), out = u / rms(u) * weight; 0:
@@ -288,7 +302,31 @@ typedef struct LlmeGatedNormOp {
     void* out; long long ldo;
     int dtype, cols, group, gate_first;
     float eps, scale;
+    int gate_act;                                            /* 0: silu(g); 1: sigmoid(g) */
+    /* with `floor` [T, cols / group] every group of y is one value wider: the extra value d stands behind the group's own, and
+     * the group is divided by max(|d|, floor) + den_eps before anything else */
+    const float* floor; long long ld_floor; float den_eps;
 } LlmeGatedNormOp;
+
+/* out = x / sqrt(mean(x^2) + eps) * gain over the rows of x: a norm on (a column range of) a product. */
+typedef struct LlmeRowNormOp {
+    const void* x; long long ldx; int x_dtype;
+    const void* gain; int gain_dtype;
+    void* out; long long ldo; int out_dtype;
+    int cols; float eps;
+} LlmeRowNormOp;
+
+/* The gates of a matrix memory with exponential gating, per request and head over the request's tokens (csrc/recurrent.cu):
+ * a_t = cap tanh(i_pre / cap), b_t = logsigmoid(cap tanh(f_pre / cap)) (cap 0: uncapped), M_t = max(b_t + M_(t-1), a_t) with M in
+ * the request's state slot ([heads] 32-bit, zero when the request starts); keep = exp(b_t + M_(t-1) - M_t), take = exp(a_t - M_t),
+ * floor = exp(-M_t). */
+typedef struct LlmeExpGatesOp {
+    const float* i_pre; const float* f_pre; long long ld_pre;
+    float cap;
+    float* state; long long state_stride;
+    float* keep; float* take; float* floor; long long ld_out;
+    int heads;
+} LlmeExpGatesOp;
 
 typedef struct LlmeExecutor LlmeExecutor;
 typedef struct LlmePlan LlmePlan;
@@ -301,7 +339,9 @@ void llme_executor_destroy(LlmeExecutor*);
  * "sigmoid_mul", "residual_add", "gelu_gather_mul", "rmsnorm_add", "latent_post", "gemm_f32_batched",
  * "latent_attention_plain", and per latent size "latent_attention_tc/<rank>", "latent_attention_tc_fits/<rank>";
  * "postnorm", "gated_act", "gemm_skinny_gated", "gemm_tc_gated", "window_post", "window_attention_plain", per pair of
- * key and value sizes "window_attention_tc/<dk>x<dv>", "moe_route", "grouped_linear", "grouped_linear_tc", "moe_combine". */
+ * key and value sizes "window_attention_tc/<dk>x<dv>", "moe_route", "grouped_linear", "grouped_linear_tc", "moe_combine";
+ * "short_conv", "rotate", "recurrence", "gated_norm", "row_norm", "exp_gates", "sigmoid_mul_grouped", "residual_add_scaled",
+ * "moe_combine_gated". */
 int llme_executor_register(LlmeExecutor*, const char* name, void* entry_point);
 /* Which implementation an operation takes.  Operations and their variants:
  *   "linear":            "auto" | "tcgen05" | "cublas" | "plain"   (bfloat16 products of 128 tokens or more / all)
@@ -390,6 +430,8 @@ public:
     int add(const LlmeRotateOp& r) { return add(LLME_OP_ROTATE, &r, sizeof r); }
     int add(const LlmeRecurrenceOp& r) { return add(LLME_OP_RECURRENCE, &r, sizeof r); }
     int add(const LlmeGatedNormOp& r) { return add(LLME_OP_GATED_NORM, &r, sizeof r); }
+    int add(const LlmeRowNormOp& r) { return add(LLME_OP_ROW_NORM, &r, sizeof r); }
+    int add(const LlmeExpGatesOp& r) { return add(LLME_OP_EXP_GATES, &r, sizeof r); }
     /* One step through the whole plan; throws with the failing record's message. */
     void run(const LlmeStep& step, cudaStream_t stream) {
         if (llme_plan_run(h_, &step, 0, -1, stream)) throw std::runtime_error(ex_.error());

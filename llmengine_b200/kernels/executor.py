@@ -13,8 +13,10 @@ F32, BF16 = 0, 1
 ROWS = {"tokens": 0, "logits": 1}
 (OP_EMBEDDING, OP_RMSNORM, OP_LINEAR, OP_LINEAR_SWIGLU, OP_QKV_POST, OP_ATTEND, OP_ATTENTION, OP_CALL, OP_LINEAR_ACT,
  OP_POINTWISE, OP_BATCHED_LINEAR, OP_RESIDUAL_ADD, OP_LATENT_ATTENTION, OP_TOKEN_SIDE, OP_POSTNORM, OP_WINDOW_ATTENTION,
- OP_MOE_ROUTE, OP_GROUPED_LINEAR, OP_MOE_COMBINE, OP_SHORT_CONV, OP_ROTATE, OP_RECURRENCE, OP_GATED_NORM) = range(1, 24)
-GATES = {"silu": 0, "clamped_swish": 1}
+ OP_MOE_ROUTE, OP_GROUPED_LINEAR, OP_MOE_COMBINE, OP_SHORT_CONV, OP_ROTATE, OP_RECURRENCE, OP_GATED_NORM, OP_ROW_NORM,
+ OP_EXP_GATES) = range(1, 26)
+GATES = {"silu": 0, "clamped_swish": 1, "gelu_tanh": 2}
+ROUTING = {"sigmoid": 0, "softmax_chosen": 1}
 ACTIVATIONS = {"xielu": 1}
 POINTWISE = {"sigmoid_mul": 1}
 
@@ -99,7 +101,7 @@ class LinearActOp(Structure):
 
 class PointwiseOp(Structure):
     _fields_ = [("what", c_int), ("dtype", c_int), ("cols", c_int), ("a", c_void_p), ("lda", c_longlong), ("b", c_void_p),
-                ("ldb", c_longlong), ("out", c_void_p), ("ldo", c_longlong), ("scale", c_float)]
+                ("ldb", c_longlong), ("out", c_void_p), ("ldo", c_longlong), ("scale", c_float), ("group", c_int)]
 
 
 class BatchedLinearOp(Structure):
@@ -110,7 +112,8 @@ class BatchedLinearOp(Structure):
 
 
 class ResidualAddOp(Structure):
-    _fields_ = [("x", c_void_p), ("a", c_void_p), ("b", c_void_p), ("dtype", c_int), ("size", c_int)]
+    _fields_ = [("x", c_void_p), ("a", c_void_p), ("b", c_void_p), ("dtype", c_int), ("size", c_int), ("a_scale", c_void_p),
+                ("b_scale", c_void_p)]
 
 
 class LatentAttentionOp(Structure):
@@ -118,7 +121,8 @@ class LatentAttentionOp(Structure):
                 ("q_rot_head_stride", c_longlong), ("c_gain", c_void_p), ("gain_dtype", c_int), ("eps", c_float),
                 ("inv_freq", c_void_p), ("rot_dims", c_int), ("q", c_void_p), ("out", c_void_p), ("dtype", c_int),
                 ("cache", c_void_p), ("cache_rows", c_longlong), ("group", c_int), ("nh", c_int), ("rank", c_int), ("rot", c_int),
-                ("scale", c_float), ("sink", c_void_p), ("scratch", c_void_p), ("scratch_floats", c_longlong)]
+                ("scale", c_float), ("sink", c_void_p), ("scratch", c_void_p), ("scratch_floats", c_longlong), ("window", c_int),
+                ("interleaved", c_int)]
 
 
 class TokenSideOp(Structure):
@@ -140,12 +144,13 @@ class WindowAttentionOp(Structure):
                 ("cache", c_void_p), ("group", c_int), ("nh", c_int), ("nkv", c_int), ("dk", c_int), ("dv", c_int),
                 ("window", c_int), ("keep_first", c_int), ("scale", c_float), ("sink", c_void_p), ("scratch", c_void_p),
                 ("scratch_floats", c_longlong), ("q_bias", c_void_p), ("k_bias", c_void_p), ("v_bias", c_void_p),
-                ("head_norm", c_int)]
+                ("head_norm", c_int), ("softcap", c_float), ("interleaved", c_int), ("in_f32", c_int)]
 
 
 class MoeRouteOp(Structure):
     _fields_ = [("logits", c_void_p), ("ld", c_longlong), ("num_experts", c_int), ("top_k", c_int), ("scale", c_float),
-                ("experts", c_void_p), ("weights", c_void_p), ("offsets", c_void_p), ("order", c_void_p), ("counts", c_void_p)]
+                ("experts", c_void_p), ("weights", c_void_p), ("offsets", c_void_p), ("order", c_void_p), ("counts", c_void_p),
+                ("mode", c_int)]
 
 
 class GroupedLinearOp(Structure):
@@ -157,7 +162,7 @@ class GroupedLinearOp(Structure):
 
 class MoeCombineOp(Structure):
     _fields_ = [("y", c_void_p), ("ldy", c_longlong), ("weights", c_void_p), ("base", c_void_p), ("out", c_void_p),
-                ("top_k", c_int), ("size", c_int)]
+                ("top_k", c_int), ("size", c_int), ("base_gate", c_void_p), ("ld_gate", c_longlong)]
 
 
 class ShortConvOp(Structure):
@@ -176,13 +181,26 @@ class RecurrenceOp(Structure):
                 ("v", c_void_p), ("ldv", c_longlong), ("v_dtype", c_int), ("gate", c_int), ("decay", c_void_p),
                 ("dt", c_void_p), ("lddt", c_longlong), ("dt_dtype", c_int), ("dt_bias", c_void_p), ("a_log", c_void_p),
                 ("skip", c_void_p), ("state", c_void_p), ("state_stride", c_longlong), ("out", c_void_p), ("ldo", c_longlong),
-                ("heads", c_int), ("n", c_int), ("p", c_int), ("scratch", c_void_p), ("scratch_floats", c_longlong)]
+                ("heads", c_int), ("n", c_int), ("p", c_int), ("scratch", c_void_p), ("scratch_floats", c_longlong),
+                ("keep", c_void_p), ("take", c_void_p), ("ld_gates", c_longlong), ("unit_column", c_int)]
 
 
 class GatedNormOp(Structure):
     _fields_ = [("y", c_void_p), ("ldy", c_longlong), ("gate", c_void_p), ("ldg", c_longlong), ("weight", c_void_p),
                 ("out", c_void_p), ("ldo", c_longlong), ("dtype", c_int), ("cols", c_int), ("group", c_int),
-                ("gate_first", c_int), ("eps", c_float), ("scale", c_float)]
+                ("gate_first", c_int), ("eps", c_float), ("scale", c_float), ("gate_act", c_int), ("floor", c_void_p),
+                ("ld_floor", c_longlong), ("den_eps", c_float)]
+
+
+class RowNormOp(Structure):
+    _fields_ = [("x", c_void_p), ("ldx", c_longlong), ("x_dtype", c_int), ("gain", c_void_p), ("gain_dtype", c_int),
+                ("out", c_void_p), ("ldo", c_longlong), ("out_dtype", c_int), ("cols", c_int), ("eps", c_float)]
+
+
+class ExpGatesOp(Structure):
+    _fields_ = [("i_pre", c_void_p), ("f_pre", c_void_p), ("ld_pre", c_longlong), ("cap", c_float), ("state", c_void_p),
+                ("state_stride", c_longlong), ("keep", c_void_p), ("take", c_void_p), ("floor", c_void_p), ("ld_out", c_longlong),
+                ("heads", c_int)]
 
 
 def _f32(t, n=None) -> bool:
@@ -310,8 +328,10 @@ def records(op, keep: List[Any]):
     if k == "pointwise":
         x, b, out = a["a"], a["b"], a["out"]
         assert x.stride(1) == 1 and out.stride(1) == 1 and (b is None or (b.stride(1) == 1 and b.dtype == x.dtype)) and out.dtype == x.dtype
+        group = int(a.get("group", 1))
+        assert group >= 1 and out.shape[1] % group == 0 and (b is None or b.shape[1] * group == out.shape[1])
         return OP_POINTWISE, PointwiseOp(POINTWISE[a["what"]], code(x.dtype), out.shape[1], x.data_ptr(), x.stride(0), ptr(b),
-                                         b.stride(0) if b is not None else 0, out.data_ptr(), out.stride(0), float(a.get("scale", 1.0)))
+                                         b.stride(0) if b is not None else 0, out.data_ptr(), out.stride(0), float(a.get("scale", 1.0)), group)
     if k == "batched_linear":
         x, w, out = a["x"], a["w"], a["out"]
         assert x.dim() == 3 and w.dim() == 3 and out.dim() == 3 and x.stride(2) == 1 and out.stride(2) == 1 and w.is_contiguous()
@@ -323,7 +343,9 @@ def records(op, keep: List[Any]):
         x, u, v = a["x"], a["a"], a["b"]
         assert x.dtype == torch.float32 and x.is_contiguous() and u.is_contiguous() and u.shape == x.shape
         assert v is None or (v.is_contiguous() and v.dtype == u.dtype and v.shape == x.shape)
-        return OP_RESIDUAL_ADD, ResidualAddOp(x.data_ptr(), u.data_ptr(), ptr(v), code(u.dtype), x.shape[1])
+        assert _f32(a.get("a_scale"), x.shape[1]) and _f32(a.get("b_scale"), x.shape[1])
+        return OP_RESIDUAL_ADD, ResidualAddOp(x.data_ptr(), u.data_ptr(), ptr(v), code(u.dtype), x.shape[1], ptr(a.get("a_scale")),
+                                              ptr(a.get("b_scale")))
     if k == "latent_attention":
         q, out, cache, kv, qr, gain = a["q"], a["out"], a["cache"], a["kv_in"], a["q_rot"], a["c_gain"]
         H, r, dr = a["num_heads"], a["kv_rank"], a["rot_dim"]
@@ -337,7 +359,7 @@ def records(op, keep: List[Any]):
             kv.data_ptr(), kv.stride(0), ptr(qr), qr.stride(0) if qr is not None else 0, qr.stride(1) if qr is not None else 0,
             gain.data_ptr(), code(gain.dtype), a["eps"], ptr(freq), a["rot_dims"], q.data_ptr(), out.data_ptr(), code(q.dtype),
             cache.data_ptr(), cache.shape[0] * cache.shape[1], a["group"], H, r, dr, a["scale"], ptr(sink), ptr(scratch),
-            scratch.numel() if scratch is not None else 0)
+            scratch.numel() if scratch is not None else 0, int(a.get("window", 0)), 1 if a.get("interleaved") else 0)
     if k == "token_side":
         x, u, v, table, wg, wp, gain, xb, g, y = (a[n] for n in ("x", "a", "b", "table", "w_gate", "w_proj", "gain", "xb", "g", "y"))
         D, dim = x.shape[1], a["dim"]
@@ -359,7 +381,8 @@ def records(op, keep: List[Any]):
     if k == "window_attention":
         qi, ki, vi, q, out, cache = a["q_in"], a["k_in"], a["v_in"], a["q"], a["out"], a["cache"]
         H, G, dk, dv = a["num_heads"], a["num_kv_heads"], a["qk_dim"], a["v_dim"]
-        assert qi.dtype == q.dtype == out.dtype == cache.dtype and qi.stride(1) == 1 and q.is_contiguous() and out.is_contiguous()
+        wide = qi.dtype == torch.float32 and q.dtype != torch.float32       # 32-bit projections (from a convolution)
+        assert q.dtype == out.dtype == cache.dtype and (wide or qi.dtype == q.dtype) and qi.stride(1) == 1 and q.is_contiguous() and out.is_contiguous()
         assert cache.is_contiguous() and qi.shape[1] == q.shape[1] == H * dk and out.shape[1] == H * dv and cache.shape[1] % (G * (dk + dv)) == 0
         assert (ki is None) == (vi is None) and (ki is None or (ki.dtype == vi.dtype == qi.dtype and ki.stride(1) == vi.stride(1) == 1
                                                               and ki.shape[1] == G * dk and vi.shape[1] == G * dv))
@@ -369,10 +392,11 @@ def records(op, keep: List[Any]):
             assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n)
         return OP_WINDOW_ATTENTION, WindowAttentionOp(
             qi.data_ptr(), ptr(ki), ptr(vi), qi.stride(0), ki.stride(0) if ki is not None else 0, vi.stride(0) if vi is not None else 0,
-            code(qi.dtype), ptr(a["q_gain"]), ptr(a["k_gain"]), a["eps"], ptr(a["inv_freq"]), a["rot_dims"], a["amplitude"],
+            code(q.dtype), ptr(a["q_gain"]), ptr(a["k_gain"]), a["eps"], ptr(a["inv_freq"]), a["rot_dims"], a["amplitude"],
             q.data_ptr(), out.data_ptr(), cache.data_ptr(), a["group"], H, G, dk, dv, a["window"], a["keep_first"], a["scale"],
             ptr(a["sink"]), ptr(a.get("scratch")), a["scratch"].numel() if a.get("scratch") is not None else 0,
-            ptr(a.get("q_bias")), ptr(a.get("k_bias")), ptr(a.get("v_bias")), 1 if a.get("head_norm") else 0)
+            ptr(a.get("q_bias")), ptr(a.get("k_bias")), ptr(a.get("v_bias")), 1 if a.get("head_norm") else 0,
+            float(a.get("softcap", 0.0)), 1 if a.get("interleaved") else 0, 1 if wide else 0)
     if k == "moe_route":
         z, ex_, wt, off, order, counts = a["logits"], a["experts"], a["weights"], a["offsets"], a["order"], a["counts"]
         assert z.dtype == wt.dtype == torch.float32 and z.stride(1) == 1 and ex_.is_contiguous() and wt.is_contiguous()
@@ -380,7 +404,7 @@ def records(op, keep: List[Any]):
         E, top = z.shape[1], a["top_k"]
         assert ex_.shape[1] == wt.shape[1] == top and off.numel() == E + 1 and counts.numel() == E and order.numel() >= ex_.shape[0] * top
         return OP_MOE_ROUTE, MoeRouteOp(z.data_ptr(), z.stride(0), E, top, a["scale"], ex_.data_ptr(), wt.data_ptr(), off.data_ptr(),
-                                        order.data_ptr(), counts.data_ptr())
+                                        order.data_ptr(), counts.data_ptr(), ROUTING[a.get("mode", "sigmoid")])
     if k == "grouped_linear":
         x, w, out, mid = a["x"], a["w"], a["out"], a["mid"]
         act = 1 if a["act"] else 0
@@ -394,7 +418,10 @@ def records(op, keep: List[Any]):
         y, wt, base, out = a["y"], a["weights"], a["base"], a["out"]
         assert y.dtype == wt.dtype == out.dtype == torch.float32 and y.stride(1) == 1 and wt.is_contiguous() and out.is_contiguous()
         assert base is None or (base.dtype == torch.float32 and base.is_contiguous() and base.shape[1] == out.shape[1])
-        return OP_MOE_COMBINE, MoeCombineOp(y.data_ptr(), y.stride(0), wt.data_ptr(), ptr(base), out.data_ptr(), wt.shape[1], out.shape[1])
+        bg = a.get("base_gate")
+        assert bg is None or (base is not None and bg.dtype == torch.float32 and bg.dim() == 2 and bg.shape[1] == 1)
+        return OP_MOE_COMBINE, MoeCombineOp(y.data_ptr(), y.stride(0), wt.data_ptr(), ptr(base), out.data_ptr(), wt.shape[1], out.shape[1],
+                                            ptr(bg), bg.stride(0) if bg is not None else 0)
     if k == "short_conv":
         x, w, b, st, out = a["x"], a["w"], a["bias"], a["state"], a["out"]
         C, K = w.shape
@@ -418,7 +445,12 @@ def records(op, keep: List[Any]):
         q, kk, v, st, out = a["q"], a["k"], a["v"], a["state"], a["out"]
         H, n, p, G = a["heads"], a["n"], a["p"], a["qk_groups"]
         assert q.dtype == kk.dtype == out.dtype == torch.float32 and q.stride(1) == kk.stride(1) == v.stride(1) == out.stride(1) == 1
-        assert q.shape[1] == kk.shape[1] == G * n and v.shape[1] == out.shape[1] == H * p and H % G == 0
+        unit = bool(a.get("unit_column"))
+        assert q.shape[1] == kk.shape[1] == G * n and out.shape[1] == H * p and v.shape[1] == H * (p - 1 if unit else p) and H % G == 0
+        keep, take = a.get("keep"), a.get("take")
+        assert (keep is None) == (take is None) and (keep is None or a.get("dt") is None)
+        for t in (keep, take):
+            assert t is None or (t.dtype == torch.float32 and t.stride(1) == 1 and t.shape[1] == H and t.stride(0) == keep.stride(0))
         assert _state(st) and tuple(st.shape[1:]) == (H, p, n)
         dt, scratch = a.get("dt"), a.get("scratch")
         assert scratch is None or (scratch.dtype == torch.float32 and scratch.is_contiguous())
@@ -426,15 +458,35 @@ def records(op, keep: List[Any]):
         for t in ("decay", "dt_bias", "a_log", "skip"):
             assert _f32(a.get(t), H)
         return OP_RECURRENCE, RecurrenceOp(q.data_ptr(), kk.data_ptr(), q.stride(0), kk.stride(0), G, v.data_ptr(), v.stride(0), code(v.dtype),
-                                           0 if dt is None else 1, ptr(a.get("decay")), ptr(dt), dt.stride(0) if dt is not None else 0,
+                                           2 if keep is not None else (0 if dt is None else 1), ptr(a.get("decay")), ptr(dt), dt.stride(0) if dt is not None else 0,
                                            code(dt.dtype) if dt is not None else 0, ptr(a.get("dt_bias")), ptr(a.get("a_log")),
                                            ptr(a.get("skip")), st.data_ptr(), st.stride(0), out.data_ptr(), out.stride(0), H, n, p,
-                                           ptr(scratch), scratch.numel() if scratch is not None else 0)
+                                           ptr(scratch), scratch.numel() if scratch is not None else 0, ptr(keep), ptr(take),
+                                           keep.stride(0) if keep is not None else 0, 1 if unit else 0)
     if k == "gated_norm":
         y, g, w, out = a["y"], a["gate"], a["weight"], a["out"]
-        cols = y.shape[1]
+        cols, floor = out.shape[1], a.get("floor")
         assert y.dtype == torch.float32 and y.stride(1) == g.stride(1) == out.stride(1) == 1 and g.dtype == out.dtype
-        assert g.shape[1] == out.shape[1] == cols and cols % a["group"] == 0 and _f32(w, cols)
+        assert g.shape[1] == cols and cols % a["group"] == 0 and _f32(w, cols)
+        groups = cols // a["group"]
+        assert y.shape[1] == (cols + groups if floor is not None else cols)
+        assert floor is None or (floor.dtype == torch.float32 and floor.stride(1) == 1 and floor.shape[1] == groups)
         return OP_GATED_NORM, GatedNormOp(y.data_ptr(), y.stride(0), g.data_ptr(), g.stride(0), ptr(w), out.data_ptr(), out.stride(0),
-                                          code(out.dtype), cols, a["group"], 1 if a["gate_first"] else 0, a["eps"], a["scale"])
+                                          code(out.dtype), cols, a["group"], 1 if a["gate_first"] else 0, a["eps"], a["scale"],
+                                          1 if a.get("gate_act", "silu") == "sigmoid" else 0, ptr(floor),
+                                          floor.stride(0) if floor is not None else 0, float(a.get("den_eps", 0.0)))
+    if k == "row_norm":
+        x, g, out = a["x"], a["gain"], a["out"]
+        assert x.stride(1) == 1 and out.stride(1) == 1 and x.shape[1] == out.shape[1] == g.numel() and g.is_contiguous()
+        return OP_ROW_NORM, RowNormOp(x.data_ptr(), x.stride(0), code(x.dtype), g.data_ptr(), code(g.dtype), out.data_ptr(), out.stride(0),
+                                      code(out.dtype), x.shape[1], a["eps"])
+    if k == "exp_gates":
+        ip, fp, st, keep, take, floor = a["i_pre"], a["f_pre"], a["state"], a["keep"], a["take"], a["floor"]
+        H = ip.shape[1]
+        for t in (ip, fp, keep, take, floor):
+            assert t.dtype == torch.float32 and t.stride(1) == 1 and t.shape[1] == H
+        assert ip.stride(0) == fp.stride(0) and keep.stride(0) == take.stride(0) == floor.stride(0)
+        assert _state(st) and tuple(st.shape[1:]) == (H,)
+        return OP_EXP_GATES, ExpGatesOp(ip.data_ptr(), fp.data_ptr(), ip.stride(0), a["cap"], st.data_ptr(), st.stride(0), keep.data_ptr(),
+                                        take.data_ptr(), floor.data_ptr(), keep.stride(0), H)
     raise ValueError(f"the executor has no record for the operation {k!r}")

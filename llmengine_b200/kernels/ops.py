@@ -198,12 +198,14 @@ class CudaOps:
                       "gelu_gather_mul": "llme_gelu_gather_mul", "rmsnorm_add": "llme_rmsnorm_add",
                       "latent_post": "llme_latent_post", "postnorm": "llme_postnorm", "gated_act": "llme_gated_act",
                       "sigmoid_mul_scaled": "llme_sigmoid_mul_scaled", "gated_act_bias": "llme_gated_act_bias",
-                      "bias_add": "llme_bias_add"},
+                      "bias_add": "llme_bias_add", "sigmoid_mul_grouped": "llme_sigmoid_mul_grouped",
+                      "residual_add_scaled": "llme_residual_add_scaled", "row_norm": "llme_row_norm"},
         "recurrent": {"short_conv": "llme_short_conv", "rotate": "llme_rotate", "recurrence": "llme_recurrence",
-                      "gated_norm": "llme_gated_norm"},
+                      "gated_norm": "llme_gated_norm", "exp_gates": "llme_exp_gates"},
         "attention_window": {"window_post": "llme_window_post", "window_attention_plain": "llme_window_attention_plain"},
         "attention_window_tc": {"window_attention_tc/{hd}": "llme_window_attention_tc"},
-        "moe": {"moe_route": "llme_moe_route", "grouped_linear": "llme_grouped_linear", "moe_combine": "llme_moe_combine"},
+        "moe": {"moe_route": "llme_moe_route", "grouped_linear": "llme_grouped_linear", "moe_combine": "llme_moe_combine",
+                "moe_combine_gated": "llme_moe_combine_gated"},
         "moe_tc": {"grouped_linear_tc": "llme_grouped_linear_tc"},
         "attention_latent": {"latent_attention_plain": "llme_latent_attention_plain"},
         "attention_latent_tc": {"latent_attention_tc/{hd}": "llme_latent_attention_tc",
@@ -243,13 +245,13 @@ class CudaOps:
             a = op.a
             if op.kind in ("embedding", "rmsnorm", "qkv_post", "attention"):
                 want("elementwise")
-            if op.kind in ("linear_act", "pointwise", "residual_add", "latent_attention", "token_side", "postnorm"):
+            if op.kind in ("linear_act", "pointwise", "residual_add", "latent_attention", "token_side", "postnorm", "row_norm"):
                 want("pointwise")
             if op.kind == "linear_swiglu" and (a.get("act", "silu") != "silu" or a.get("bias") is not None):
                 want("pointwise")
             if op.kind == "linear" and a.get("bias") is not None:
                 want("pointwise")
-            if op.kind in ("short_conv", "rotate", "recurrence", "gated_norm"):
+            if op.kind in ("short_conv", "rotate", "recurrence", "gated_norm", "exp_gates"):
                 want("recurrent")
             if op.kind == "window_attention":
                 want("attention_window")
