@@ -93,13 +93,15 @@ def matrix_memory(h, w, pre, m, eps, round_to, carry=None):
     maximum M that starts at 0: M_t = max(b + M_(t-1), a);  S_t = exp(b + M_(t-1) - M_t) S_(t-1) + exp(a - M_t) k v^T and
     n_t the same with k alone;  o_t = S_t^T q / (max(|n_t . q|, exp(-M_t)) + 1e-6).  Every head's o is divided by its root
     mean square; the heads, side by side, are multiplied by a weight and by sigmoid(W_g h).  Returns [T, H P] and the carry."""
-    H, d, P, cap = m["heads"], m["dim"], m["vdim"], float(m["gate_cap"])
+    H, d, P, cap = m["heads"], m["dim"], m["vdim"], m.get("gate_cap")
     T = h.shape[0]
     q = _r(h @ w[pre + "q"].t(), round_to).view(T, H, d) * (d ** -0.5)
     k = _r(h @ w[pre + "k"].t(), round_to).view(T, H, d)
     v = _r(h @ w[pre + "v"].t(), round_to).view(T, H, P)
-    a = cap * torch.tanh((h @ w[pre + "i"].t() + w[pre + "i.b"]) / cap)
-    b = log_sigmoid(cap * torch.tanh((h @ w[pre + "f"].t() + w[pre + "f.b"]) / cap))
+    a, b = h @ w[pre + "i"].t() + w[pre + "i.b"], h @ w[pre + "f"].t() + w[pre + "f.b"]
+    if cap:                                                       # (a model without a cap has uncapped gates)
+        a, b = cap * torch.tanh(a / cap), cap * torch.tanh(b / cap)
+    b = log_sigmoid(b)
     if carry is None:
         S, n, M = torch.zeros(H, d, P, dtype=h.dtype), torch.zeros(H, d, dtype=h.dtype), torch.zeros(H, dtype=h.dtype)
     else:
@@ -173,12 +175,16 @@ def gated_ff(h, w, pre, act, round_to):
     return _r(act(g) * u, round_to) @ w[pre + "down"].t()
 
 
-def routed_ff(h, w, pre, mlp, round_to):
+def routed_ff(h, w, pre, mlp, round_to, gaps=None):
     """z = W_router h + b; the `top` largest logits choose the experts, whose weights are the softmax over the chosen
-    logits alone; output = sum of weight_e expert_e(h), plus the shared expert times sigmoid(W_sg h) (one number a token)."""
+    logits alone; output = sum of weight_e expert_e(h), plus the shared expert times sigmoid(W_sg h) (one number a token).
+    `gaps` (a list) receives, per token, how far the last chosen logit lies above the first one not chosen."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     z = h @ w[pre + "router"].t() + w[pre + "router.b"]
     val, idx = torch.topk(z, top, dim=-1)
+    if gaps is not None and top < E:
+        both = torch.topk(z, top + 1, dim=-1).values
+        gaps.append((both[:, top - 1] - both[:, top]).to(torch.float32))
     wt = torch.softmax(val, -1)
     out = torch.zeros(h.shape[0], w[pre + "e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
@@ -199,6 +205,8 @@ class PlainFunevik:
         self.w: Dict[str, torch.Tensor] = {n: t.to(self.ft) for n, t in
                                            read_safetensors(os.path.join(model_dir, "model.safetensors")).items()}
         self.round_to = round_to
+        self._gaps: list = []
+        self.gaps = torch.zeros(0)
 
     def mixer(self, i: int, L: dict, h: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
         w, rt, eps = self.w, self.round_to, self.cfg["norm"]["eps"]
@@ -218,13 +226,14 @@ class PlainFunevik:
         if mlp["kind"] == "dense":
             return gated_ff(h, self.w, pre, gelu_tanh, self.round_to)
         if mlp["kind"] == "moe":
-            return routed_ff(h, self.w, pre, mlp, self.round_to)
+            return routed_ff(h, self.w, pre, mlp, self.round_to, self._gaps)
         raise ValueError(mlp["kind"])
 
     def forward(self, ids: Sequence[int], layers_out: Optional[list] = None) -> torch.Tensor:
         cfg, w, rt = self.cfg, self.w, self.round_to
         eps = cfg["norm"]["eps"]
         pos = torch.arange(len(ids))
+        self._gaps = []
         x = w["embed"][torch.tensor(list(ids), dtype=torch.long)] * float(cfg["embedding"]["scale"])
         for i, L in enumerate(cfg["layers"]):
             p = f"l{i}."
@@ -235,6 +244,8 @@ class PlainFunevik:
             x = x + y
             if layers_out is not None:
                 layers_out.append(x.clone())
+        # per position, the closest call any router of the model made on it
+        self.gaps = torch.stack(self._gaps).amin(0) if self._gaps else torch.full((len(ids),), float("inf"))
         return _r(rms_norm(x, w["final.norm"], eps), rt) @ w["head"].t()
 
     def logits(self, ids: Sequence[int]) -> torch.Tensor:
