@@ -508,7 +508,7 @@ def main() -> int:
     ap.add_argument("--breakdown", action="store_true",
                     help="instead of the bench line, print the time of every operation of a layer (decode at --batch "
                          "inside a CUDA graph, and a 2,048-token prefill), timed with CUDA events")
-    ap.add_argument("--design", default=None, choices=["bepuzen", "torisun", "vifelix"],
+    ap.add_argument("--design", default=None, choices=["bepuzen", "torisun", "vifelix", "funevik"],
                     help="instead of the bench line: this design beside the grouped-query model of equal size (prefill and "
                          "decode tokens/s, and every record of a layer against its roofline)")
     ap.add_argument("--size", default=None, help="with --design: one of its sizes alone (2048, 4096)")

@@ -1,4 +1,4 @@
-"""A design beside its closest existing model at equal size (`python bench.py --design bepuzen | torisun | vifelix`).
+"""A design beside its closest existing model at equal size (`python bench.py --design bepuzen | torisun | vifelix | funevik`).
 
 For each size: prefill of one 2,048-token prompt and decode at batch 1 / 8 / 64 over 2,048 cached tokens, tokens/s,
 for the design and for the grouped-query model of the same width, depth and (active) weight count per layer;
@@ -76,6 +76,24 @@ def vifelix_shape(width: int, heads: int, kv_heads: int, ff: int, ssm_heads: int
             "layers": [mamba, mamba, par, mamba, mamba, par]}
 
 
+def funevik_shape(width: int, heads: int, kv_heads: int, ff: int, experts: int, top: int, expert_ff: int, memory_heads: int,
+                  window: int = 1024, dim: int = 128, vocab: int = 32768) -> Dict[str, Any]:
+    """Six layers, every layer with two norms and two scale vectors: three matrix memories (heads of 128 x 256), two latent
+    attentions (queries through a latent of 1,536, keys and values through one of 512, a shared rotated part of 64, a window)
+    and one grouped-query attention with short convolutions and capped scores; dense and routed feed-forwards in turn."""
+    mem = {"heads": memory_heads, "dim": 128, "vdim": 256, "gate_cap": 15.0}
+    lat = {"heads": heads, "dim": dim, "rot_dim": 64, "vdim": dim, "kv_rank": 512, "q_rank": 1536, "scale": (dim + 64) ** -0.5,
+           "rot": {"base": 10000.0, "dims": 64}, "mask": {"size": window}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "conv": 4, "softcap": 50.0,
+           "rot": {"base": 10000.0, "dims": dim // 2}}
+    dense = {"kind": "dense", "ff": ff}
+    routed = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": expert_ff}}
+    kinds = [("mlstm", mem, dense), ("latent_attention", lat, routed), ("mlstm", mem, dense), ("attention", att, routed),
+             ("mlstm", mem, None), ("latent_attention", lat, dense)]
+    return {"architecture": "Funevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": width ** 0.5},
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in kinds]}
+
+
 # 32-bit multiply-adds outside the tensor cores: 148 SMs x 128 lanes x 2 x 1.965 GHz (nominal), the compute ceiling of a
 # recurrence whose state and inputs are 32-bit
 FP32_TFLOPS = 74.4
@@ -92,6 +110,10 @@ SIZES = {
 VIFELIX_SIZES = {
     "2048": (6, vifelix_shape(2048, 16, 4, 5504, 64, 8), gqa_shape(6, 2048, 16, 5504)),
     "4096": (6, vifelix_shape(4096, 32, 8, 10944, 128, 16), gqa_shape(6, 4096, 32, 10944)),
+}
+FUNEVIK_SIZES = {
+    "2048": (6, funevik_shape(2048, 16, 4, 5504, 32, 4, 1024, 8), gqa_shape(6, 2048, 16, 5504)),
+    "4096": (6, funevik_shape(4096, 32, 8, 10944, 64, 4, 2048, 16), gqa_shape(6, 4096, 32, 10944)),
 }
 CACHED, PROMPT = 2048, 2048
 
@@ -121,9 +143,16 @@ def record_cost(op, T: int, keys_per_row: float, cache_rows: float):
         w = a["w"]
         return f"batched_linear {w.shape[0]}x{w.shape[1]}x{w.shape[2]}", 2.0 * T * w.numel(), _bytes(w) + T * w.shape[0] * (w.shape[1] + w.shape[2]) * el
     if k == "latent_attention":
-        H, r, dr = a["num_heads"], a["kv_rank"], a["rot_dim"]
-        return (f"latent attention {H} heads, rows of {r}+{dr}", 2.0 * T * H * keys_per_row * (2 * r + dr),
-                cache_rows * (r + dr) * el + T * H * (2 * r + dr) * el)
+        H, r, dr, W = a["num_heads"], a["kv_rank"], a["rot_dim"], a.get("window", 0)
+        keys, rows_read = keys_per_row, cache_rows
+        if W and T > cache_rows / 2:                                     # a prompt: the mean over positions 0 .. ctx - 1
+            n = int(2 * keys_per_row - 1)
+            keys = sum(min(i + 1, W) for i in range(n)) / n
+        elif W:
+            keys = min(keys_per_row, W)
+            rows_read = cache_rows * keys / keys_per_row
+        return (f"latent attention {H} heads, rows of {r}+{dr}" + (f", window {W}" if W else ""), 2.0 * T * H * keys * (2 * r + dr),
+                rows_read * (r + dr) * el + T * H * (2 * r + dr) * el)
     if k in ("attention", "attend"):
         nh, nkv, hd = a["num_heads"], a["num_kv_heads"], a["head_dim"]
         return (f"attention {nh}/{nkv} heads of {hd}", 4.0 * T * nh * hd * keys_per_row, cache_rows * 2 * nkv * hd * el + 2 * T * nh * hd * el)
@@ -165,7 +194,11 @@ def record_cost(op, T: int, keys_per_row: float, cache_rows: float):
     if k == "pointwise":
         return f"pointwise {a['what']}", 0.0, 3 * T * a["out"].shape[1] * el
     if k == "residual_add":
-        return "residual add", 0.0, T * a["x"].shape[1] * 16
+        return "residual add" + (" with scale vectors" if a.get("a_scale") is not None else ""), 0.0, T * a["x"].shape[1] * 16
+    if k == "row_norm":
+        return f"norm on a product's columns ({a['x'].shape[1]})", 0.0, T * a["x"].shape[1] * 2 * el
+    if k == "exp_gates":
+        return f"exponential gates, {a['i_pre'].shape[1]} heads", 0.0, T * a["i_pre"].shape[1] * 5 * 4
     requests = T if T <= cache_rows / 2 else 1                            # a decode step has one token a request
     if k == "short_conv":
         C, K = a["w"].shape
@@ -176,11 +209,12 @@ def record_cost(op, T: int, keys_per_row: float, cache_rows: float):
         return f"rotation into 32-bit, {cols} columns", 0.0, T * cols * (el + 4)
     if k == "recurrence":
         H, n, p, G = a["heads"], a["n"], a["p"], a["qk_groups"]
-        return (f"recurrence {H} heads, state {n}x{p}" + (", decay per token" if a.get("dt") is not None else ", fixed decay"),
+        return (f"recurrence {H} heads, state {n}x{p}" + (", decay per token" if a.get("dt") is not None else
+                                                          ", given gates" if a.get("keep") is not None else ", fixed decay"),
                 4.0 * T * H * n * p * FP32_SHARE, requests * 2 * H * n * p * 4 + T * (2 * G * n * 4 + H * p * (a["v"].element_size() + 4)))
     if k == "gated_norm":
         cols = a["y"].shape[1]
-        return f"gate + norm in groups of {a['group']}", 0.0, T * cols * (4 + 2 * el)
+        return f"gate + norm in groups of {a['group']}" + (", normalised" if a.get("floor") is not None else ""), 0.0, T * cols * (4 + 2 * el)
     return k, 0.0, 0.0
 
 
@@ -325,7 +359,7 @@ def run(args, pk) -> int:
 
     import torch
     design_name = getattr(args, "design", None) or "bepuzen"
-    table_of_sizes = {"bepuzen": SIZES, "torisun": TORISUN_SIZES, "vifelix": VIFELIX_SIZES}[design_name]
+    table_of_sizes = {"bepuzen": SIZES, "torisun": TORISUN_SIZES, "vifelix": VIFELIX_SIZES, "funevik": FUNEVIK_SIZES}[design_name]
     global FP32_SHARE
     FP32_SHARE = pk["bf16_tflops"] / FP32_TFLOPS
     sizes = [args.size] if getattr(args, "size", None) else list(table_of_sizes)

@@ -87,12 +87,17 @@ def causal_conv(u: torch.Tensor, taps: torch.Tensor) -> torch.Tensor:
 
 
 # --------------------------------------------------------------------- mixers
-def matrix_memory(h, w, pre, m, eps, round_to, carry=None):
+def matrix_memory(h, w, pre, m, eps, round_to, carry=None, calls=None):
     """The matrix memory with exponential gates.  Per head: q = W_q h / sqrt(d), k = W_k h, v = W_v h; log gates
     a = cap tanh((W_i h + b_i) / cap) (input) and b = logsigmoid(cap tanh((W_f h + b_f) / cap)) (forget); a running
     maximum M that starts at 0: M_t = max(b + M_(t-1), a);  S_t = exp(b + M_(t-1) - M_t) S_(t-1) + exp(a - M_t) k v^T and
     n_t the same with k alone;  o_t = S_t^T q / (max(|n_t . q|, exp(-M_t)) + 1e-6).  Every head's o is divided by its root
-    mean square; the heads, side by side, are multiplied by a weight and by sigmoid(W_g h).  Returns [T, H P] and the carry."""
+    mean square; the heads, side by side, are multiplied by a weight and by sigmoid(W_g h).  Returns [T, H P] and the carry.
+
+    After the division by its root mean square a head's output at a request's FIRST token is v_0 / rms(v_0) times the sign of
+    k_0 . q_0 (the memory holds one term): a step function of the input.  `calls` (a list) receives, per token, how far the
+    model is from that step: 8 |cos(q_0, k_0)|, the least over the heads, at the first token, infinity elsewhere (in the units
+    of the routers' margins, so that one threshold serves both kinds of close call)."""
     H, d, P, cap = m["heads"], m["dim"], m["vdim"], m.get("gate_cap")
     T = h.shape[0]
     q = _r(h @ w[pre + "q"].t(), round_to).view(T, H, d) * (d ** -0.5)
@@ -102,6 +107,11 @@ def matrix_memory(h, w, pre, m, eps, round_to, carry=None):
     if cap:                                                       # (a model without a cap has uncapped gates)
         a, b = cap * torch.tanh(a / cap), cap * torch.tanh(b / cap)
     b = log_sigmoid(b)
+    if calls is not None:
+        away = torch.full((T,), float("inf"))
+        if carry is None and T:
+            away[0] = 8.0 * float(torch.nn.functional.cosine_similarity(q[0], k[0], dim=-1).abs().min())
+        calls.append(away)
     if carry is None:
         S, n, M = torch.zeros(H, d, P, dtype=h.dtype), torch.zeros(H, d, dtype=h.dtype), torch.zeros(H, dtype=h.dtype)
     else:
@@ -212,7 +222,7 @@ class PlainFunevik:
         w, rt, eps = self.w, self.round_to, self.cfg["norm"]["eps"]
         m, pre = L["mixer"], f"l{i}.mix."
         if L["type"] == "mlstm":
-            heads = matrix_memory(h, w, pre, m, eps, rt)[0]
+            heads = matrix_memory(h, w, pre, m, eps, rt, calls=self._gaps)[0]
         elif L["type"] == "latent_attention":
             heads = latent_attention(h, w, pre, m, eps, pos, rt)
         elif L["type"] == "attention":
@@ -244,7 +254,7 @@ class PlainFunevik:
             x = x + y
             if layers_out is not None:
                 layers_out.append(x.clone())
-        # per position, the closest call any router of the model made on it
+        # per position, the closest call any router (or the first token of any memory) of the model made on it
         self.gaps = torch.stack(self._gaps).amin(0) if self._gaps else torch.full((len(ids),), float("inf"))
         return _r(rms_norm(x, w["final.norm"], eps), rt) @ w["head"].t()
 
