@@ -37,16 +37,17 @@ def reference_logits(model_dir: str, reqs: Dict[str, List[int]], dtype: str):
     rounding to bfloat16 where the engine stores bfloat16; it is the reference because a mixture of experts is not
     continuous, and only a run that rounds where the engine rounds takes the same choices.  The yardstick of the tolerance is
     the model's own sensitivity to rounding (the distance between the rounded and the unrounded plain run): the engine must
-    stay within one and a half yardsticks of the rounded run."""
+    stay within two yardsticks of the rounded run (the models here have up to six layers, three kinds of mixer and routers in
+    most layers, and the engine also rounds the attention's probabilities and the queries carried into the latent space)."""
     plain = PlainFunevik(model_dir)
     rounded = PlainFunevik(model_dir, round_to=torch.bfloat16)
-    keep_away_from_close_calls(rounded if dtype == "bfloat16" else plain, reqs, 0.5 if dtype == "bfloat16" else 2e-4)
+    keep_away_from_close_calls(rounded if dtype == "bfloat16" else plain, reqs, 0.25 if dtype == "bfloat16" else 2e-4)
     ref = {r: plain.logits(ids) for r, ids in reqs.items()}
     if dtype != "bfloat16":
         return ref, TOL_F32 * max(1.0, max(float(v.abs().max()) for v in ref.values()) / 10.0)
     ref16 = {r: rounded.logits(ids) for r, ids in reqs.items()}
     inherent = max(float((ref16[r] - ref[r]).abs().max()) for r in ref)
-    return ref16, max(5e-3, 1.5 * inherent)
+    return ref16, max(5e-3, 2.0 * inherent)
 
 
 def replay_all_schedules(model_dir: str, cfg: dict, dtype: str, lens: Sequence[int], page: int, ops, device: str,
