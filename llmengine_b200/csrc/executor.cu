@@ -71,7 +71,7 @@ typedef int (*SigmoidMulGroupedFn)(const void*, long long, const void*, long lon
 typedef int (*ResidualAddScaledFn)(float*, const void*, const void*, int, void*, int, int, int, const float*, const float*, cudaStream_t);
 typedef int (*MoeCombineGatedFn)(const float*, long long, const float*, const float*, float*, int, int, int, const float*, long long, cudaStream_t);
 typedef int (*RowNormFn)(const void*, long long, int, const void*, int, void*, long long, int, int, int, float, cudaStream_t);
-typedef int (*ExpGatesFn)(const LlmeExpGatesArgs*, cudaStream_t);
+typedef int (*ExpGatesFn)(const LlmeExpGatesArgs*, int, cudaStream_t);
 typedef int (*GemmF32BatchedFn)(const float*, const void*, int, float*, int, int, int, long long, long long, long long, int, long long,
                                 long long, long long, cudaStream_t);
 
@@ -775,7 +775,7 @@ int op_exp_gates(LlmeExecutor& ex, const LlmeExpGatesOp& o, const LlmeStep& s, c
     if (!f) return ex.fail("no exp_gates kernel is registered");
     LlmeExpGatesArgs a = {o.i_pre, o.f_pre, o.ld_pre, o.cap, o.state, o.state_stride, o.keep, o.take, o.floor, o.ld_out, s.cu_q_lens, s.state_slots,
                           s.num_requests, o.heads};
-    return ex.launched(f(&a, st), "exp_gates");
+    return ex.launched(f(&a, s.max_portion_len > 1 ? s.max_portion_len : 1, st), "exp_gates");
 }
 
 int op_moe_route(LlmeExecutor& ex, const LlmeMoeRouteOp& o, const LlmeStep& s, cudaStream_t st) {

@@ -679,59 +679,70 @@ LLME_API int llme_recurrence(const LlmeRecurrenceArgs* args, cudaStream_t stream
 }
 
 // ----------------------------------------------------------------------------- exponential gates with a running maximum
-// One warp per (request, head), 32 tokens at a time: every lane forms the two log gates of its token (the transcendental
-// part, side by side), then all lanes walk the 32 running maxima in the tokens' order (an addition and a maximum each, the
-// operands handed round the warp), and every lane forms its token's three outputs.  The walk is the plain one, so a token's
-// values do not depend on how its request was cut into steps.
+// One block per (request, head), GATE_TILE tokens at a time: every thread forms the two log gates of its token (the
+// transcendental part, side by side, into shared memory), one thread walks the running maxima of the tile in the tokens' order
+// (an addition and a maximum a token, operands from shared memory), and every thread forms its token's three outputs.  The walk
+// is the plain one, so a token's values do not depend on how its request was cut into steps.  A step of single tokens takes one
+// warp per block.
 __device__ __forceinline__ float log_sigmoid32(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
+constexpr int GATE_TILE = 256;
+
 __global__ void exp_gates_kernel(LlmeExpGatesArgs a) {
+    __shared__ float ga[GATE_TILE], gb[GATE_TILE], mx[GATE_TILE + 1];
     pdl_launch_dependents();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), r = blockIdx.y;
-    if (h >= a.heads) return;
+    const int h = blockIdx.x, r = blockIdx.y, tile = blockDim.x;
     const int first = a.cu_q_lens[r], last = a.cu_q_lens[r + 1];
-    if (last <= first) return;
+    if (last <= first) return;                                      // (uniform over the block)
     float* kept = a.state + (size_t)a.state_slots[r] * a.state_stride + h;
-    float M = *kept;
-    for (int t0 = first; t0 < last; t0 += 32) {
-        const int t = t0 + lane;
-        float ga = 0.0f, gb = 0.0f;
+    if (threadIdx.x == 0) mx[0] = *kept;
+    for (int t0 = first; t0 < last; t0 += tile) {
+        const int t = t0 + threadIdx.x, count = min(tile, last - t0);
+        float va = 0.0f, vb = 0.0f;
         if (t < last) {
-            ga = a.i_pre[(size_t)t * a.ld_pre + h];
-            gb = a.f_pre[(size_t)t * a.ld_pre + h];
+            va = a.i_pre[(size_t)t * a.ld_pre + h];
+            vb = a.f_pre[(size_t)t * a.ld_pre + h];
             if (a.cap > 0.0f) {
-                ga = a.cap * tanhf(ga / a.cap);
-                gb = a.cap * tanhf(gb / a.cap);
+                va = a.cap * tanhf(va / a.cap);
+                vb = a.cap * tanhf(vb / a.cap);
             }
-            gb = log_sigmoid32(gb);
+            vb = log_sigmoid32(vb);
+            ga[threadIdx.x] = va;
+            gb[threadIdx.x] = vb;
         }
-        float before = M, after = M;
-        const int count = min(32, last - t0);
-        for (int u = 0; u < count; ++u) {
-            const float au = __shfl_sync(0xffffffffu, ga, u), bu = __shfl_sync(0xffffffffu, gb, u);
-            const float next = fmaxf(bu + M, au);
-            if (u == lane) { before = M; after = next; }
-            M = next;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float M = mx[0];
+#pragma unroll 8
+            for (int u = 0; u < count; ++u) {
+                M = fmaxf(gb[u] + M, ga[u]);
+                mx[u + 1] = M;                                      // mx[u]: the maximum before token u, mx[u + 1]: behind it
+            }
         }
+        __syncthreads();
+        const float before = mx[threadIdx.x < count ? threadIdx.x : 0], after = mx[threadIdx.x < count ? threadIdx.x + 1 : 0];
+        const float carried = mx[count];
+        __syncthreads();
+        if (threadIdx.x == 0) mx[0] = carried;
         if (t < last) {
-            a.keep[(size_t)t * a.ld_out + h] = expf(gb + before - after);
-            a.take[(size_t)t * a.ld_out + h] = expf(ga - after);
+            a.keep[(size_t)t * a.ld_out + h] = expf(vb + before - after);
+            a.take[(size_t)t * a.ld_out + h] = expf(va - after);
             a.floor[(size_t)t * a.ld_out + h] = expf(-after);
         }
     }
-    if (lane == 0) *kept = M;
+    __syncthreads();
+    if (threadIdx.x == 0) *kept = mx[0];
 }
 
-LLME_API int llme_exp_gates(const LlmeExpGatesArgs* args, cudaStream_t stream) {
+LLME_API int llme_exp_gates(const LlmeExpGatesArgs* args, int max_len, cudaStream_t stream) {
     const LlmeExpGatesArgs& a = *args;
     if (a.requests <= 0 || a.heads <= 0) return 0;
     if (!a.i_pre || !a.f_pre || !a.state || !a.keep || !a.take || !a.floor || !a.cu_q_lens || !a.state_slots) LLME_REFUSE("exp_gates: null pointer");
     if (a.cap < 0.0f) LLME_REFUSE("exp_gates: a negative cap");
     if (a.requests > 65535) LLME_REFUSE("exp_gates: too many requests for one launch");
-    const int warps = a.heads >= 4 ? 4 : a.heads;
-    llme_launch(exp_gates_kernel, dim3((a.heads + warps - 1) / warps, a.requests), dim3(32 * warps), 0, stream, a);
+    const int threads = max_len <= 32 ? 32 : (max_len <= 128 ? 128 : GATE_TILE);
+    llme_launch(exp_gates_kernel, dim3(a.heads, a.requests), dim3(threads), 0, stream, a);
     LLME_LAUNCH_STATUS();
 }
 

@@ -202,10 +202,14 @@ class RoutedExperts(Part):
 
     def load_weights(self, t: Dict[str, torch.Tensor]) -> None:
         rows = [t[self.name("router")]] + ([t[self.name("shared.sg")]] if self.shared_gate else [])
+        used = sum(r.shape[0] for r in rows)
+        pad = -used % 8                 # rows of zeros up to a multiple of 8: the product's 32-bit output rows then start on 32 bytes
+        if pad:
+            rows.append(rows[0].new_zeros(pad, self.hidden))
         self.w_router = torch.cat(rows, 0).contiguous()
         if self.router_bias:
             b = t[self.name("router.b")].float()
-            self.b_router = torch.cat([b, b.new_zeros(1)]).contiguous() if self.shared_gate else b.contiguous()
+            self.b_router = torch.cat([b, b.new_zeros(self.w_router.shape[0] - self.E)]).contiguous()
         self.w_gate_up = torch.stack([torch.cat([t[self.name(f"e{e}.gate")], t[self.name(f"e{e}.up")]], 0)
                                       for e in range(self.E)]).contiguous()
         self.w_down = torch.stack([t[self.name(f"e{e}.down")] for e in range(self.E)]).contiguous()
