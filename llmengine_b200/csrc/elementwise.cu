@@ -83,10 +83,12 @@ LLME_API int llme_embedding(const int* ids, const void* table, int table_dtype, 
 // ----------------------------------------------------------------------------- RMS norm (+ residual add)
 // For output row i (source row r = rows ? rows[i] : i):
 //   v = x[r] (+ delta[r], stored back into x[r]);  y[i] = (v * 1/sqrt(mean(v^2) + eps)) * gain.
-// One block per row; the sum of squares is reduced in a fixed order.
+// One block per row; the sum of squares is reduced in a fixed order.  With `gain2` / `out2` the same normed row is also
+// written with a second gain to a second place (two norms of the same x: a layer whose sublayers each have their own).
 template <typename D, typename G, typename O, bool HAS_DELTA>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const D* __restrict__ delta, const G* __restrict__ gain,
-                               O* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+                               O* __restrict__ out, const int* __restrict__ rows, int hidden, float eps,
+                               const G* __restrict__ gain2, O* __restrict__ out2) {
     pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
     pdl_wait();                // everything below reads or writes what earlier kernels touch
     __shared__ float scratch[32];
@@ -109,6 +111,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const D* __restrict__ delt
     for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
         // same thread wrote xr[j] above, so the re-read sees the sum
         o[j] = from_f32<O>((xr[j] * rinv) * to_f32(gain[j]));
+        if (out2) out2[(size_t)i * hidden + j] = from_f32<O>((xr[j] * rinv) * to_f32(gain2[j]));
     }
 }
 
@@ -136,7 +139,8 @@ template <> struct Vec4<__nv_bfloat16> {
 
 template <typename D, typename G, typename O, bool HAS_DELTA, int V>
 __global__ void rmsnorm_vec_kernel(float* __restrict__ x, const D* __restrict__ delta, const G* __restrict__ gain,
-                                   O* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+                                   O* __restrict__ out, const int* __restrict__ rows, int hidden, float eps,
+                                   const G* __restrict__ gain2, O* __restrict__ out2) {
     pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
     pdl_wait();                // everything below reads or writes what earlier kernels touch
     __shared__ float scratch[32];
@@ -172,58 +176,77 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ x, const D* __restrict__ 
 #pragma unroll
     for (int k = 0; k < V; ++k) {
         const int j = threadIdx.x + k * blockDim.x;
-        if (j < groups)
+        if (j < groups) {
             Vec4<O>::store(o + 4 * j, make_float4((v[k].x * rinv) * g[k].x, (v[k].y * rinv) * g[k].y,
                                                   (v[k].z * rinv) * g[k].z, (v[k].w * rinv) * g[k].w));
+            if (out2) {
+                const float4 h = Vec4<G>::load(gain2 + 4 * j);
+                Vec4<O>::store(out2 + (size_t)i * hidden + 4 * j, make_float4((v[k].x * rinv) * h.x, (v[k].y * rinv) * h.y,
+                                                                              (v[k].z * rinv) * h.z, (v[k].w * rinv) * h.w));
+            }
+        }
     }
 }
 
 template <typename D, typename G, typename O, bool HAS_DELTA>
 static bool launch_rmsnorm_vec(float* x, const void* delta, const void* gain, void* out, const int* rows,
-                               int n_out, int hidden, float eps, cudaStream_t s) {
+                               int n_out, int hidden, float eps, cudaStream_t s, const void* gain2, void* out2) {
     if (hidden % 4 || hidden > 16384) return false;
-    if (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)gain | (uintptr_t)out) % 16) return false;
+    if (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)gain | (uintptr_t)out | (uintptr_t)gain2 | (uintptr_t)out2) % 16) return false;
     const int groups = hidden / 4;
     // few rows: short dependency chains matter more than occupancy, so spread the row over many threads
     if (groups <= 256)
-        llme_launch(rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 1>, dim3(n_out), dim3(((groups + 31) / 32) * 32), 0, s, x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
+        llme_launch(rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 1>, dim3(n_out), dim3(((groups + 31) / 32) * 32), 0, s, x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps, (const G*)gain2, (O*)out2);
     else if (groups <= 1024)
-        llme_launch(rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 2>, dim3(n_out), dim3((((groups + 1) / 2 + 31) / 32) * 32), 0, s, x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
+        llme_launch(rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 2>, dim3(n_out), dim3((((groups + 1) / 2 + 31) / 32) * 32), 0, s, x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps, (const G*)gain2, (O*)out2);
     else
-        llme_launch(rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 4>, dim3(n_out), dim3((((groups + 3) / 4 + 31) / 32) * 32), 0, s, x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
+        llme_launch(rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 4>, dim3(n_out), dim3((((groups + 3) / 4 + 31) / 32) * 32), 0, s, x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps, (const G*)gain2, (O*)out2);
     return true;
 }
 
 template <typename D, typename G, typename O, bool HAS_DELTA>
 static void launch_rmsnorm(float* x, const void* delta, const void* gain, void* out, const int* rows,
-                           int n_out, int hidden, float eps, cudaStream_t s) {
-    if (launch_rmsnorm_vec<D, G, O, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s)) return;
+                           int n_out, int hidden, float eps, cudaStream_t s, const void* gain2, void* out2) {
+    if (launch_rmsnorm_vec<D, G, O, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s, gain2, out2)) return;
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-    llme_launch(rmsnorm_kernel<D, G, O, HAS_DELTA>, dim3(n_out), dim3(threads), 0, s, x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
+    llme_launch(rmsnorm_kernel<D, G, O, HAS_DELTA>, dim3(n_out), dim3(threads), 0, s, x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps, (const G*)gain2, (O*)out2);
 }
 
 template <typename D, bool HAS_DELTA>
 static int dispatch_rmsnorm(float* x, const void* delta, const void* gain, int gain_dtype, void* out, int out_dtype,
-                            const int* rows, int n_out, int hidden, float eps, cudaStream_t s) {
-    if (gain_dtype == LLME_F32 && out_dtype == LLME_F32) launch_rmsnorm<D, float, float, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s);
-    else if (gain_dtype == LLME_F32 && out_dtype == LLME_BF16) launch_rmsnorm<D, float, __nv_bfloat16, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s);
-    else if (gain_dtype == LLME_BF16 && out_dtype == LLME_F32) launch_rmsnorm<D, __nv_bfloat16, float, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s);
-    else if (gain_dtype == LLME_BF16 && out_dtype == LLME_BF16) launch_rmsnorm<D, __nv_bfloat16, __nv_bfloat16, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s);
+                            const int* rows, int n_out, int hidden, float eps, cudaStream_t s, const void* gain2 = nullptr,
+                            void* out2 = nullptr) {
+    if (gain_dtype == LLME_F32 && out_dtype == LLME_F32) launch_rmsnorm<D, float, float, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s, gain2, out2);
+    else if (gain_dtype == LLME_F32 && out_dtype == LLME_BF16) launch_rmsnorm<D, float, __nv_bfloat16, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s, gain2, out2);
+    else if (gain_dtype == LLME_BF16 && out_dtype == LLME_F32) launch_rmsnorm<D, __nv_bfloat16, float, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s, gain2, out2);
+    else if (gain_dtype == LLME_BF16 && out_dtype == LLME_BF16) launch_rmsnorm<D, __nv_bfloat16, __nv_bfloat16, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s, gain2, out2);
     else LLME_REFUSE("rmsnorm: unsupported gain/out dtype %d/%d", gain_dtype, out_dtype);
     LLME_LAUNCH_STATUS();
 }
 
 // x [*, hidden] 32-bit (updated in place when delta is given); delta nullable; rows nullable
 // (n_out source-row indices); out [n_out, hidden].
+LLME_API int llme_rmsnorm_pair(float* x, const void* delta, int delta_dtype, const void* gain, int gain_dtype,
+                               void* out, int out_dtype, const int* rows, int n_out, int hidden, float eps,
+                               const void* gain2, void* out2, cudaStream_t stream);
+
 LLME_API int llme_rmsnorm(float* x, const void* delta, int delta_dtype, const void* gain, int gain_dtype,
                           void* out, int out_dtype, const int* rows, int n_out, int hidden, float eps,
                           cudaStream_t stream) {
+    return llme_rmsnorm_pair(x, delta, delta_dtype, gain, gain_dtype, out, out_dtype, rows, n_out, hidden, eps, nullptr, nullptr, stream);
+}
+
+// The same with a second gain and a second place for the same normed rows (both of the first one's types), or neither.
+LLME_API int llme_rmsnorm_pair(float* x, const void* delta, int delta_dtype, const void* gain, int gain_dtype,
+                               void* out, int out_dtype, const int* rows, int n_out, int hidden, float eps,
+                               const void* gain2, void* out2, cudaStream_t stream) {
     if (n_out <= 0) return 0;
     if (!x || !gain || !out || hidden <= 0) LLME_REFUSE("rmsnorm: null pointer or non-positive size");
+    if ((gain2 == nullptr) != (out2 == nullptr)) LLME_REFUSE("rmsnorm: a second gain comes with a second place");
     if (!(eps > 0.0f)) LLME_REFUSE("rmsnorm: eps must be positive");
-    if (!delta) return dispatch_rmsnorm<float, false>(x, nullptr, gain, gain_dtype, out, out_dtype, rows, n_out, hidden, eps, stream);
-    if (delta_dtype == LLME_F32) return dispatch_rmsnorm<float, true>(x, delta, gain, gain_dtype, out, out_dtype, rows, n_out, hidden, eps, stream);
-    if (delta_dtype == LLME_BF16) return dispatch_rmsnorm<__nv_bfloat16, true>(x, delta, gain, gain_dtype, out, out_dtype, rows, n_out, hidden, eps, stream);
+    if (!delta) return dispatch_rmsnorm<float, false>(x, nullptr, gain, gain_dtype, out, out_dtype, rows, n_out, hidden, eps, stream, gain2, out2);
+    if (delta_dtype == LLME_F32) return dispatch_rmsnorm<float, true>(x, delta, gain, gain_dtype, out, out_dtype, rows, n_out, hidden, eps, stream, gain2, out2);
+    if (delta_dtype == LLME_BF16) return dispatch_rmsnorm<__nv_bfloat16, true>(x, delta, gain, gain_dtype, out, out_dtype, rows, n_out, hidden, eps, stream, gain2, out2);
     LLME_REFUSE("rmsnorm: unsupported delta dtype %d", delta_dtype);
 }
 

@@ -67,6 +67,7 @@ typedef int (*ShortConvFn)(const LlmeShortConvArgs*, int, cudaStream_t);
 typedef int (*RotateFn)(const LlmeRotateArgs*, cudaStream_t);
 typedef int (*RecurrenceFn)(const LlmeRecurrenceArgs*, cudaStream_t);
 typedef int (*GatedNormFn)(const LlmeGatedNormArgs*, cudaStream_t);
+typedef int (*RmsNormPairFn)(float*, const void*, int, const void*, int, void*, int, const int*, int, int, float, const void*, void*, cudaStream_t);
 typedef int (*SigmoidMulGroupedFn)(const void*, long long, const void*, long long, void*, long long, int, int, int, float, int, cudaStream_t);
 typedef int (*ResidualAddScaledFn)(float*, const void*, const void*, int, void*, int, int, int, const float*, const float*, cudaStream_t);
 typedef int (*MoeCombineGatedFn)(const float*, long long, const float*, const float*, float*, int, int, int, const float*, long long, cudaStream_t);
@@ -316,6 +317,12 @@ int op_rmsnorm(LlmeExecutor& ex, const LlmeRmsNormOp& o, const LlmeStep& s, cuda
     auto* f = (RmsNormFn)ex.find("rmsnorm");
     if (!f) return ex.fail("no rmsnorm kernel is registered");
     const bool some = o.rows == LLME_ROWS_LOGITS;
+    if (o.gain2) {
+        auto* g = (RmsNormPairFn)ex.find("rmsnorm_pair");
+        if (!g) return ex.fail("no rmsnorm kernel with a second gain is registered");
+        return ex.launched(g(o.x, o.delta, o.delta_dtype, o.gain, o.gain_dtype, o.out, o.out_dtype, some ? s.logit_rows : nullptr,
+                             rows_of(s, o.rows), o.size, o.eps, o.gain2, o.out2, st), "rmsnorm");
+    }
     return ex.launched(f(o.x, o.delta, o.delta_dtype, o.gain, o.gain_dtype, o.out, o.out_dtype, some ? s.logit_rows : nullptr,
                          rows_of(s, o.rows), o.size, o.eps, st), "rmsnorm");
 }

@@ -54,10 +54,12 @@ class Plan:
         self._add("embedding", table=table, out=out, scale=float(scale))
 
     def rmsnorm(self, x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
-                delta: Optional[torch.Tensor] = None, rows: str = ROWS_TOKENS) -> None:
+                delta: Optional[torch.Tensor] = None, rows: str = ROWS_TOKENS, gain2: Optional[torch.Tensor] = None,
+                out2: Optional[torch.Tensor] = None) -> None:
         """x += delta (if given), out = rmsnorm(x) * gain; `rows` = "logits": only the step's wanted rows,
-        gathered into the first rows of `out`."""
-        self._add("rmsnorm", x=x, gain=gain, eps=float(eps), out=out, delta=delta, rows=rows)
+        gathered into the first rows of `out`.  With `gain2` and `out2` (the types of `gain` and `out`) the same normed
+        rows also go, times the second gain, to the second place: two norms of the same x in one pass."""
+        self._add("rmsnorm", x=x, gain=gain, eps=float(eps), out=out, delta=delta, rows=rows, gain2=gain2, out2=out2)
         if delta is not None:
             self.note_copy(x, None)
 

@@ -94,6 +94,7 @@ typedef struct LlmeRmsNormOp {
     void* out; int out_dtype;
     int size; float eps;
     int rows;                  /* LLME_ROWS_TOKENS: every row; LLME_ROWS_LOGITS: the step's logit rows only */
+    const void* gain2; void* out2;   /* a second gain and place for the same normed rows (the types of the first), or NULL */
 } LlmeRmsNormOp;
 
 typedef struct LlmeLinearOp {

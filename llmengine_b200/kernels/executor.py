@@ -59,7 +59,8 @@ class EmbeddingOp(Structure):
 
 class RmsNormOp(Structure):
     _fields_ = [("x", c_void_p), ("delta", c_void_p), ("delta_dtype", c_int), ("gain", c_void_p), ("gain_dtype", c_int),
-                ("out", c_void_p), ("out_dtype", c_int), ("size", c_int), ("eps", c_float), ("rows", c_int)]
+                ("out", c_void_p), ("out_dtype", c_int), ("size", c_int), ("eps", c_float), ("rows", c_int), ("gain2", c_void_p),
+                ("out2", c_void_p)]
 
 
 class LinearOp(Structure):
@@ -281,8 +282,11 @@ def records(op, keep: List[Any]):
     if k == "rmsnorm":
         x, d, g, out = a["x"], a["delta"], a["gain"], a["out"]
         assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and (d is None or d.is_contiguous())
+        g2, out2 = a.get("gain2"), a.get("out2")
+        assert (g2 is None) == (out2 is None) and (g2 is None or (g2.dtype == g.dtype and g2.is_contiguous() and g2.numel() == g.numel()
+                                                                  and out2.dtype == out.dtype and out2.is_contiguous() and out2.shape == out.shape))
         return OP_RMSNORM, RmsNormOp(x.data_ptr(), ptr(d), code(d.dtype) if d is not None else 0, g.data_ptr(), code(g.dtype),
-                                     out.data_ptr(), code(out.dtype), x.shape[1], a["eps"], ROWS[a["rows"]])
+                                     out.data_ptr(), code(out.dtype), x.shape[1], a["eps"], ROWS[a["rows"]], ptr(g2), ptr(out2))
     if k == "linear":
         x, w, out = a["x"], a["w"], a["out"]
         assert x.stride(1) == 1 and w.stride(1) == 1 and w.shape[1] == x.shape[1] and (out is None or out.stride(1) == 1)

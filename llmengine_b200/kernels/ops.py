@@ -192,7 +192,7 @@ class CudaOps:
 
     _ENTRY_POINTS = {
         "elementwise": {"embedding": "llme_embedding", "rmsnorm": "llme_rmsnorm", "qkv_post": "llme_qkv_post",
-                        "swiglu": "llme_swiglu", "embedding_scaled": "llme_embedding_scaled"},
+                        "swiglu": "llme_swiglu", "embedding_scaled": "llme_embedding_scaled", "rmsnorm_pair": "llme_rmsnorm_pair"},
         "gemm_f32": {"gemm_f32": "llme_gemm_nt_f32", "gemm_f32_batched": "llme_gemm_nt_f32_batched"},
         "pointwise": {"xielu": "llme_xielu", "sigmoid_mul": "llme_sigmoid_mul", "residual_add": "llme_residual_add",
                       "gelu_gather_mul": "llme_gelu_gather_mul", "rmsnorm_add": "llme_rmsnorm_add",

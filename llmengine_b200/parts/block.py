@@ -134,12 +134,18 @@ class ParallelResidualBlock(Part):
 
     def emit(self, plan: Plan, x: torch.Tensor, delta: Optional[torch.Tensor], cache):
         hidden = x.shape[1]
-        h = emit_norm(plan, self.norm, x, delta=delta)
+        h2 = None
+        if self.ffn_norm is not None and hasattr(self.norm, "pairs_with") and self.norm.pairs_with(self.ffn_norm):
+            h, h2 = self.norm.emit_pair(plan, self.ffn_norm, x, delta=delta)      # both norms of the same x in one pass
+        else:
+            h = emit_norm(plan, self.norm, x, delta=delta)
         a = emit_mixer(plan, self.mixer, h, cache, hidden)
         b = None
         if self.ffn is not None:
             # a second norm of the same x goes to a workspace of its own: the mixer's input may still be needed
-            if self.ffn_norm is None:
+            if h2 is not None:
+                pass
+            elif self.ffn_norm is None:
                 h2 = h
             elif hasattr(self.ffn_norm, "emit"):
                 h2 = self.ffn_norm.emit(plan, x, out_name="normed_second")

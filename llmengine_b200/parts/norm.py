@@ -35,6 +35,19 @@ class RMSNorm(Part):
         plan.rmsnorm(x, self.gain, self.eps, out, delta=delta, rows=rows)
         return out
 
+    def pairs_with(self, other) -> bool:
+        """Whether `other` norms the same rows in the same way but for its gain, so that one pass can serve both."""
+        return (isinstance(other, RMSNorm) and other.size == self.size and other.eps == self.eps and self.gain is not None
+                and other.gain is not None and other.gain.dtype == self.gain.dtype)
+
+    def emit_pair(self, plan: Plan, other: "RMSNorm", x: torch.Tensor, delta: Optional[torch.Tensor] = None,
+                  other_name: str = "normed_second"):
+        """Both norms of the same x (this one's and `other`'s) as one record; returns the two outputs."""
+        out = self.rt.workspace("normed", self.size, self.rt.dtype)
+        out2 = self.rt.workspace(other_name, self.size, self.rt.dtype)
+        plan.rmsnorm(x, self.gain, self.eps, out, delta=delta, gain2=other.gain, out2=out2)
+        return out, out2
+
     def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor] = None,
                 out_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         from ..engine.batch import StepBatch

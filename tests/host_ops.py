@@ -27,7 +27,7 @@ class HostOps:
         out.copy_(table[ids.long()].float() * scale)
         return out
 
-    def rmsnorm(self, x, gain, eps, out, delta=None, rows=None):
+    def rmsnorm(self, x, gain, eps, out, delta=None, rows=None, gain2=None, out2=None):
         if delta is not None:
             if rows is None:
                 x += delta.float()
@@ -36,6 +36,8 @@ class HostOps:
         src = x if rows is None else x[rows.long()]
         ms = (src * src).sum(-1, keepdim=True) / src.shape[-1]
         out.copy_(((src * (1.0 / torch.sqrt(ms + eps))) * gain.float()).to(out.dtype))
+        if out2 is not None:
+            out2.copy_(((src * (1.0 / torch.sqrt(ms + eps))) * gain2.float()).to(out2.dtype))
         return out
 
     def qkv_post(self, *, q_in, k_in, v_in, num_heads, num_kv_heads, head_dim, q_gain=None, k_gain=None, eps=0.0,
@@ -415,7 +417,8 @@ class HostPlan:
             elif k == "rmsnorm":
                 some = a["rows"] == "logits"
                 o.rmsnorm(a["x"][:T], a["gain"], a["eps"], a["out"][:n_rows(a["rows"])], delta=cut(a["delta"]),
-                          rows=batch.logit_rows if some else None)
+                          rows=batch.logit_rows if some else None, gain2=a.get("gain2"),
+                          out2=a["out2"][:n_rows(a["rows"])] if a.get("out2") is not None else None)
             elif k == "linear":
                 n = n_rows(a["rows"])
                 if n:

@@ -135,7 +135,8 @@ def test_normalised_gated_norm_kernel(dtype, tol, groups, group):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 3e-2)])
 def test_small_records_of_the_design(dtype, tol):
-    """A norm on a column range of a product (narrow and wider than a warp's share); a sigmoid gate with one value per head;
+    """A norm on a column range of a product (narrow and wider than a warp's share); two norms of the same rows as one record;
+    a sigmoid gate with one value per head;
     contributions times scale vectors in the residual add; the gated activation with gelu in its tanh form."""
     ops = _ops()
     g = torch.Generator().manual_seed(4)
@@ -149,6 +150,15 @@ def test_small_records_of_the_design(dtype, tol):
         want = rms_norm(wide[:, 5:5 + C].float(), gain.float(), 1e-5)
         assert float((out[:T, 2:2 + C].float().cpu() - want).abs().max()) < tol * 3 and float(out[T].abs().max()) == 0.0
         assert float(out[:, :2].abs().max()) == 0.0 and float(out[:, 2 + C:].abs().max()) == 0.0
+    for D in (20, 64, 1100, 4096):              # two norms of the same rows in one pass (scalar and 16-byte forms), with the pending add
+        x, delta = torch.randn(T, D, generator=g), torch.randn(T, D, generator=g).to(dtype)
+        g1, g2 = 1 + 0.2 * torch.randn(D, generator=g), 1 + 0.2 * torch.randn(D, generator=g)
+        xd, o1, o2 = x.to(DEV), torch.zeros(T, D, dtype=dtype, device=DEV), torch.zeros(T, D, dtype=dtype, device=DEV)
+        _run(ops, lambda p: p.rmsnorm(xd, g1.to(DEV), 1e-5, o1, delta=delta.to(DEV), gain2=g2.to(DEV), out2=o2), _batch([T], [0]))
+        summed = x + delta.float()
+        assert float((xd.cpu() - summed).abs().max()) < 1e-6
+        for got, gain in ((o1, g1), (o2, g2)):
+            assert float((got.float().cpu() - rms_norm(summed, gain, 1e-5)).abs().max()) < tol * 3
     H, dv = 3, 10
     a, s = torch.randn(T, H * dv, generator=g).to(dtype), torch.randn(T, H + 2, generator=g).to(dtype)
     place, sd = torch.zeros(T, H * dv, dtype=dtype, device=DEV), s.to(DEV)
