@@ -689,7 +689,8 @@ __device__ __forceinline__ float log_sigmoid32(float z) { return fminf(z, 0.0f) 
 constexpr int GATE_TILE = 256;
 
 __global__ void exp_gates_kernel(LlmeExpGatesArgs a) {
-    __shared__ float ga[GATE_TILE], gb[GATE_TILE], mx[GATE_TILE + 1];
+    __shared__ __align__(16) float ga[GATE_TILE], gb[GATE_TILE];
+    __shared__ float mx[GATE_TILE + 8];
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.x, r = blockIdx.y, tile = blockDim.x;
@@ -713,11 +714,23 @@ __global__ void exp_gates_kernel(LlmeExpGatesArgs a) {
         }
         __syncthreads();
         if (threadIdx.x == 0) {
+            // eight tokens' operands go to registers at once, so that the walk itself waits for no load: an addition and
+            // a maximum a token.  mx[u]: the maximum before token u, mx[u + 1]: behind it.
             float M = mx[0];
-#pragma unroll 8
-            for (int u = 0; u < count; ++u) {
-                M = fmaxf(gb[u] + M, ga[u]);
-                mx[u + 1] = M;                                      // mx[u]: the maximum before token u, mx[u + 1]: behind it
+#pragma unroll 2
+            for (int u0 = 0; u0 < count; u0 += 8) {
+                const float4 a0 = *(const float4*)&ga[u0], a1 = *(const float4*)&ga[u0 + 4];
+                const float4 b0 = *(const float4*)&gb[u0], b1 = *(const float4*)&gb[u0 + 4];
+                const float va8[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                const float vb8[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                float r8[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    M = u0 + i < count ? fmaxf(vb8[i] + M, va8[i]) : M;      // (what lies behind the last token is not read as a number)
+                    r8[i] = M;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mx[u0 + i + 1] = r8[i];
             }
         }
         __syncthreads();
@@ -792,16 +805,18 @@ __global__ void __launch_bounds__(128) gated_norm_block_kernel(LlmeGatedNormArgs
     const float* y = a.y + (size_t)t * a.ldy + (a.floor ? c0 + gi : c0);
     const T* g = (const T*)a.gate + (size_t)t * a.ldg + c0;
     T* o = (T*)a.out + (size_t)t * a.ldo + c0;
-    const float den = a.floor ? fmaxf(fabsf(y[a.group]), a.floor[(size_t)t * a.ld_floor + gi]) + a.den_eps : 1.0f;
     float u[8], gate[8], ss = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int c = threadIdx.x + blockDim.x * i;
-        u[i] = c < a.group ? (a.floor ? y[c] / den : y[c]) : 0.0f;
+        u[i] = c < a.group ? y[c] : 0.0f;
         gate[i] = c < a.group ? to_f32(g[c]) : 0.0f;
     }
+    // (the normaliser and its floor are asked for with the row's values, not before them)
+    const float den = a.floor ? fmaxf(fabsf(y[a.group]), a.floor[(size_t)t * a.ld_floor + gi]) + a.den_eps : 1.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
+        if (a.floor) u[i] = u[i] / den;
         gate[i] = gate32(gate[i], a.gate_act);
         if (a.gate_first) u[i] *= gate[i];
         ss += u[i] * u[i];

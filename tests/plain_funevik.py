@@ -197,10 +197,10 @@ def routed_ff(h, w, pre, mlp, round_to, gaps=None):
         gaps.append((both[:, top - 1] - both[:, top]).to(torch.float32))
     wt = torch.softmax(val, -1)
     out = torch.zeros(h.shape[0], w[pre + "e0.down"].shape[0], dtype=h.dtype)
-    for t in range(h.shape[0]):
-        for c in range(top):
-            e = int(idx[t, c])
-            out[t] += wt[t, c] * gated_ff(h[t:t + 1], w, f"{pre}e{e}.", silu, round_to)[0]
+    for c in range(top):                                   # a token's choices are added in their order
+        for e in idx[:, c].unique().tolist():
+            rows = idx[:, c] == e
+            out[rows] += wt[rows, c, None] * gated_ff(h[rows], w, f"{pre}e{e}.", silu, round_to)
     if mlp.get("shared") is not None:
         out = out + gated_ff(h, w, pre + "shared.", silu, round_to) * torch.sigmoid(h @ w[pre + "shared.sg"].t())
     return out

@@ -240,7 +240,7 @@ BIG = model(131, 128, 1e-6, 11.0, [
     ("A", TINY_A, 16, [70, 33, 100, 1, 19, 45, 64]),
     ("B", TINY_B, 8, [2, 5, 64, 130, 200, 48]),
     ("M", ONLY_MEMORY, 64, [150, 3, 40, 64, 7]),
-    ("BIG", BIG, 64, [300, 129, 40, 420, 128, 17]),
+    ("BIG", BIG, 64, [200, 129, 40, 300, 128, 17]),
     ("BIG16", BIG, 16, [260, 3, 141, 64]),
 ])
 def test_replay_gpu(tmp_path, name, cfg, page, lens, dtype, kernels):
