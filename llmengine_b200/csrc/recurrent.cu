@@ -709,9 +709,10 @@ __global__ void exp_gates_kernel(LlmeExpGatesArgs a) {
                 vb = a.cap * tanhf(vb / a.cap);
             }
             vb = log_sigmoid32(vb);
-            ga[threadIdx.x] = va;
-            gb[threadIdx.x] = vb;
         }
+        // behind the step's last token stands what changes nothing: max(0 + M, -inf) = M
+        ga[threadIdx.x] = t < last ? va : -INFINITY;
+        gb[threadIdx.x] = t < last ? vb : 0.0f;
         __syncthreads();
         if (threadIdx.x == 0) {
             // eight tokens' operands go to registers at once, so that the walk itself waits for no load: an addition and
@@ -726,7 +727,7 @@ __global__ void exp_gates_kernel(LlmeExpGatesArgs a) {
                 float r8[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    M = u0 + i < count ? fmaxf(vb8[i] + M, va8[i]) : M;      // (what lies behind the last token is not read as a number)
+                    M = fmaxf(vb8[i] + M, va8[i]);
                     r8[i] = M;
                 }
 #pragma unroll
