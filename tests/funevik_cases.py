@@ -16,8 +16,8 @@ TOL_F32 = 3e-4          # for logits of order one to ten (only the order of sums
 def keep_away_from_close_calls(model: PlainFunevik, reqs: Dict[str, List[int]], margin: float) -> None:
     """Changes the requests IN PLACE until the model makes no close call on them: where the last chosen expert's logit lies
     less than `margin` above the first one not chosen, rounding decides which expert a token uses, and where a memory's
-    first query is nearly orthogonal to its first key, rounding decides the sign of that head's first output; no comparison
-    can rest on either.  The token at the first such position is exchanged for the next one of the vocabulary
+    query is nearly orthogonal to what the memory holds (its first token; a token behind a forget gate that emptied it),
+    rounding decides the direction of that head's output; no comparison can rest on either.  The token at the first such position is exchanged for the next one of the vocabulary
     (positions before it are not affected: the model is causal)."""
     vocab = model.cfg["vocab"]
     for r, ids in reqs.items():

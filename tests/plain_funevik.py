@@ -94,10 +94,13 @@ def matrix_memory(h, w, pre, m, eps, round_to, carry=None, calls=None):
     n_t the same with k alone;  o_t = S_t^T q / (max(|n_t . q|, exp(-M_t)) + 1e-6).  Every head's o is divided by its root
     mean square; the heads, side by side, are multiplied by a weight and by sigmoid(W_g h).  Returns [T, H P] and the carry.
 
-    After the division by its root mean square a head's output at a request's FIRST token is v_0 / rms(v_0) times the sign of
-    k_0 . q_0 (the memory holds one term): a step function of the input.  `calls` (a list) receives, per token, how far the
-    model is from that step: 8 |cos(q_0, k_0)|, the least over the heads, at the first token, infinity elsewhere (in the units
-    of the routers' margins, so that one threshold serves both kinds of close call)."""
+    After the division by its root mean square only the direction of S_t^T q_t is left of a head's output.  Where q_t is nearly
+    orthogonal to what the memory holds, that direction is decided by rounding: at a request's first token, and wherever the
+    forget gate has just emptied the memory, S_t is one term k v^T and the output is v / rms(v) times the SIGN of k . q_t, a step
+    function of the input.  `calls` (a list) receives, per token, how far the model is from such a point: 2.5 sqrt(d) |S_t^T q_t| /
+    (|S_t| |q_t|) (Frobenius and Euclidean norms; for a memory of one term that is 2.5 sqrt(d) |cos(q, k)|, about 2.5 for a
+    query in general position), the least over the heads, in the units of the routers' margins, so that one threshold serves
+    both kinds of close call: a margin of 0.25 keeps a query twenty-five times farther from orthogonal than rounding moves it."""
     H, d, P, cap = m["heads"], m["dim"], m["vdim"], m.get("gate_cap")
     T = h.shape[0]
     q = _r(h @ w[pre + "q"].t(), round_to).view(T, H, d) * (d ** -0.5)
@@ -107,11 +110,7 @@ def matrix_memory(h, w, pre, m, eps, round_to, carry=None, calls=None):
     if cap:                                                       # (a model without a cap has uncapped gates)
         a, b = cap * torch.tanh(a / cap), cap * torch.tanh(b / cap)
     b = log_sigmoid(b)
-    if calls is not None:
-        away = torch.full((T,), float("inf"))
-        if carry is None and T:
-            away[0] = 8.0 * float(torch.nn.functional.cosine_similarity(q[0], k[0], dim=-1).abs().min())
-        calls.append(away)
+    away = torch.full((T,), float("inf"))
     if carry is None:
         S, n, M = torch.zeros(H, d, P, dtype=h.dtype), torch.zeros(H, d, dtype=h.dtype), torch.zeros(H, dtype=h.dtype)
     else:
@@ -124,8 +123,13 @@ def matrix_memory(h, w, pre, m, eps, round_to, carry=None, calls=None):
         n = keep[:, None] * n + take[:, None] * k[t]
         M = M_new
         num = torch.einsum("adp,ad->ap", S, q[t])
+        if calls is not None:
+            hold = S.flatten(1).norm(dim=-1) * q[t].norm(dim=-1)
+            away[t] = 2.5 * math.sqrt(d) * float((num.norm(dim=-1) / hold.clamp_min(1e-30)).min())
         den = torch.maximum((n * q[t]).sum(-1).abs(), torch.exp(-M)) + 1e-6
         o[t] = num / den[:, None]
+    if calls is not None:
+        calls.append(away)
     o = unit_rms(o, eps).reshape(T, H * P) * w[pre + "norm"]
     return o * torch.sigmoid(_r(h @ w[pre + "g"].t(), round_to)), (S, n, M)
 
@@ -254,7 +258,7 @@ class PlainFunevik:
             x = x + y
             if layers_out is not None:
                 layers_out.append(x.clone())
-        # per position, the closest call any router (or the first token of any memory) of the model made on it
+        # per position, the closest call any router or memory of the model made on it
         self.gaps = torch.stack(self._gaps).amin(0) if self._gaps else torch.full((len(ids),), float("inf"))
         return _r(rms_norm(x, w["final.norm"], eps), rt) @ w["head"].t()
 

@@ -227,7 +227,7 @@ def test_each_mixer_alone(tmp_path, name, cfg, dtype):
 BIG = model(131, 128, 1e-6, 11.0, [
     layer("latent_attention", latent(4, 32, 32, 32, 128, 96, 0.125, size=70, base=5000.0, dims=16), moe(8, 2, 64, shared=96)),
     layer("mlstm", memory(4, 64, 32, cap=15.0), dense(192)),
-    layer("attention", attention(4, 2, 64, 32, 0.11, 4, base=5000.0, dims=32, softcap=20.0), moe(8, 3, 48)),
+    layer("attention", attention(4, 2, 64, 32, 0.11, 4, base=5000.0, dims=32, softcap=20.0), dense(96)),
     layer("mlstm", memory(2, 128, 64, cap=15.0)),
     layer("latent_attention", latent(8, 16, 16, 16, 64, 64, 0.2, base=700.0)),
     layer("attention", attention(2, 1, 128, 128, 0.09, 2, base=100.0, dims=64, size=33), dense(160)),
@@ -240,7 +240,7 @@ BIG = model(131, 128, 1e-6, 11.0, [
     ("A", TINY_A, 16, [70, 33, 100, 1, 19, 45, 64]),
     ("B", TINY_B, 8, [2, 5, 64, 130, 200, 48]),
     ("M", ONLY_MEMORY, 64, [150, 3, 40, 64, 7]),
-    ("BIG", BIG, 64, [200, 129, 40, 300, 128, 17]),
+    ("BIG", BIG, 64, [200, 129, 40, 260, 128, 17]),
     ("BIG16", BIG, 16, [260, 3, 141, 64]),
 ])
 def test_replay_gpu(tmp_path, name, cfg, page, lens, dtype, kernels):
